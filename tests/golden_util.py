@@ -1,0 +1,48 @@
+"""Shared helpers for tests that read the golden fixtures written by tests/golden/make_golden.py."""
+import os
+
+import numpy as np
+import torch
+
+from oracle.ladder_oracle import OracleConfig
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TINY = dict(block_size=128, vocab_size=512, n_layer=3, n_head=4, n_local_heads=2, dim=256,
+            intermediate_size=512, rope_base=500000)
+DESYNC_PATTERN = [{"attention": False, "mlp": True}, {"attention": True, "mlp": False},
+                  {"attention": False, "mlp": False}]
+INITS = {"quiet": dict(std=0.02), "loud": dict(std=0.2, norm_mean=1.0, norm_std=0.2)}
+BATCH, PROMPT, NEW = 2, 12, 5
+SEED = 4242
+VARIANTS = [("float32", 1, "quiet"), ("float32", 2, "loud"), ("bfloat16", 1, "loud"), ("bfloat16", 2, "quiet")]
+FAMILIES = ("ladder", "dense", "parallel", "desync")
+
+
+def load(tp):
+    return np.load(os.path.join(GOLDEN_DIR, f"reference_tp{tp}.npz"))
+
+
+def tiny_config(family):
+    return OracleConfig(**TINY, reduce_pattern=DESYNC_PATTERN if family == "desync" else None)
+
+
+def rel_err(a, b):
+    """||a-b|| / ||b|| over the whole tensor, in fp64."""
+    a = torch.as_tensor(a).double()
+    b = torch.as_tensor(b).double()
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def replay(forward, gold, key):
+    """Teacher-forced replay of a golden case through `forward(idx, input_pos) -> logits`.
+    Returns the stacked last-position logits [NEW, B, V] (fp32) and row 0 of the prefill logits."""
+    prompt = torch.from_numpy(gold[key + "/prompt"])
+    fed = torch.from_numpy(gold[key + "/fed"])
+    x = prompt.view(1, -1).repeat(BATCH, 1)
+    logits = forward(x, torch.arange(PROMPT))
+    steps = [logits[:, -1].float().cpu()]
+    prefill_row0 = logits[0].float().cpu()
+    for n in range(NEW - 1):
+        logits = forward(fed[:, n:n + 1], torch.tensor([PROMPT + n], dtype=torch.int32))
+        steps.append(logits[:, -1].float().cpu())
+    return torch.stack(steps), prefill_row0
