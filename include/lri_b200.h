@@ -1,0 +1,170 @@
+/*
+ * lri_b200.h - C ABI of the B200 (sm_100a) kernels behind the tensor-parallel decode/prefill step.
+ *
+ * The reference project is pure Python (its kernels are library calls and one Triton kernel),
+ * so it has no FFI of its own; each entry point below names the reference code it replaces
+ * (paths relative to the reference repository root).  A Python binding (ctypes) passes
+ * `tensor.data_ptr()` values and the raw handle of the current CUDA stream.
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  Every pointer is a DEVICE pointer unless it says "host".
+ *   - The caller owns all memory.  No entry point allocates device memory or synchronises the
+ *     device unless its comment says so; work is enqueued on `stream`.
+ *   - `dtype` is LRI_BF16 or LRI_FP16 (activations, weights and caches share it); all
+ *     accumulation is fp32 and results are rounded once to `dtype` where the reference's
+ *     nn.Linear / elementwise op would round.
+ *   - Matrices are row-major.  Weights have the nn.Linear layout [out_features, in_features].
+ *   - Positions are read on the device from `input_pos` (int32 when pos_is_i64 == 0, int64
+ *     otherwise), never from a host scalar, so a captured CUDA graph stays valid when the caller
+ *     advances the position tensor in place (benchmark.py:209-217).
+ *   - Return value: LRI_OK or a negative lri_status; lri_last_error() gives the message of the
+ *     calling thread's last failure.  The reference's convention is a Python assert/exception
+ *     (gpt_fast/utils.py:52, 155-162); the binding raises RuntimeError on a negative status.
+ */
+#ifndef LRI_B200_H_
+#define LRI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* lri_stream_t; /* a cudaStream_t */
+
+enum lri_dtype { LRI_BF16 = 0, LRI_FP16 = 1 };
+
+enum lri_status {
+  LRI_OK = 0,
+  LRI_ERR_ARG = -1,         /* null pointer, non-positive extent, inconsistent sizes */
+  LRI_ERR_ALIGN = -2,       /* pointer or row pitch not aligned as the kernel needs */
+  LRI_ERR_UNSUPPORTED = -3, /* shape or dtype outside what the kernels are built for */
+  LRI_ERR_CUDA = -4,        /* a CUDA runtime/driver call failed (message has the CUDA text) */
+  LRI_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  LRI_ERR_TIMEOUT = -6,     /* a bounded device-side wait gave up (peer flag, mbarrier) */
+  LRI_ERR_NO_DEVICE = -7    /* no usable sm_100 device */
+};
+
+/* GEMM back end for M > 8 rows.  AUTO picks tcgen05 when the shape allows it. */
+enum lri_gemm_backend { LRI_GEMM_AUTO = 0, LRI_GEMM_TCGEN05 = 1, LRI_GEMM_SIMT = 2 };
+
+const char* lri_last_error(void);
+int lri_version(void);
+/* Selects the GEMM back end used by the linear-layer entry points (process-wide). */
+int lri_set_gemm_backend(int backend);
+/* Number of kernels this library has launched from the calling process so far. */
+int64_t lri_launch_count(void);
+/* The tcgen05 GEMM bounds every mbarrier wait; a wait that gives up records its site in a
+ * device status word.  Reads and clears it (synchronous copy): LRI_OK or LRI_ERR_TIMEOUT. */
+int lri_gemm_status(void);
+
+/* ---- F1: residual add + RMSNorm -------------------------------------------------------
+ * residual_out = round(round(residual * residual_scale) + add1) [+ add2, rounded again];
+ * normed_out   = round(residual_out * rsqrt(mean(residual_out^2) + eps)) * weight.
+ * add1, add2 may be NULL (no add); weight/normed_out may be NULL (add only); residual_out may
+ * be NULL (norm only) or alias residual.  residual_scale != 1 is the desync block's x / tp.
+ * Replaces: the Triton add kernel gpt_fast/gpt_ladder_TP.py:364-377 (launched :331, :348),
+ * the final three-way add gpt_ladder_TP.py:280, RMSNorm.forward gpt_fast/utils.py:62-78 and
+ * the `y + x / tp_world_size` of gpt_fast/gpt_desync_TP.py:366-382. */
+int lri_add_rmsnorm(int dtype, const void* residual, const void* add1, const void* add2,
+                    float residual_scale, const void* weight, float eps, void* residual_out,
+                    void* normed_out, int64_t rows, int dim, lri_stream_t stream);
+
+/* ---- embedding gather ------------------------------------------------------------------
+ * out[i, :] = table[idx[i], :].  idx is int64 when idx_is_i64 != 0, else int32.
+ * Replaces: self.tok_embeddings(idx), gpt_fast/gpt_ladder_TP.py:256. */
+int lri_embedding(int dtype, const void* table, const void* idx, int idx_is_i64, void* out,
+                  int64_t n_tokens, int dim, int64_t vocab, lri_stream_t stream);
+
+/* ---- F5 / F7: linear layer y = x W^T (+ addend) ------------------------------------------
+ * x [M, K], w [N, K], y [M, N].  addend (may be NULL) is added after y's own rounding and the
+ * sum rounded again (the parallel block's `w2(...) + y`, gpt_fast/utils.py:385).  M <= 8 runs
+ * the weight-streaming GEMV; larger M the tcgen05 GEMM.  workspace is unused today (pass
+ * NULL, 0).  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
+ * 258, 384-385 and gpt_fast/gpt_ladder_TP.py:283. */
+int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M,
+               int N, int K, void* workspace, size_t workspace_bytes, lri_stream_t stream);
+
+/* ---- F2: QKV projection + RoPE + KV-cache write ----------------------------------------
+ * x [B*S, K]; wqkv [(n_head + 2 n_kv) * head_dim, K] with rows [q heads | k heads | v heads];
+ * rope_table [table_rows, head_dim/2, 2] = (cos, sin) in `dtype`; input_pos [S].  The table row
+ * of token s is input_pos[s], or s itself when table_gathered != 0 (the caller already indexed
+ * the table by position, as the reference's forward does: freqs_cis[input_pos]).
+ * q_out [B, S, n_head, head_dim] receives the rotated queries; rotated keys and the values are
+ * written to k_cache / v_cache [B_max, n_kv, smax, head_dim] at [b, h, input_pos[s], :].
+ * Rotation is over adjacent pairs in fp32 from the rounded projection, as the reference does.
+ * A position outside [0, min(smax, table_rows)) is skipped (nothing is written for it).
+ * M = B*S > 8 needs workspace of lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) bytes.
+ * Replaces: gpt_fast/utils.py:187-198 (wqkv, split, apply_rotary_emb) and KVCache.update
+ * utils.py:50-59, 249-250. */
+size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim);
+int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void* rope_table,
+                         const void* input_pos, int pos_is_i64, void* q_out, void* k_cache,
+                         void* v_cache, int B, int S, int K, int n_head, int n_kv, int head_dim,
+                         int64_t smax, int64_t table_rows, int table_gathered, void* workspace,
+                         size_t workspace_bytes, lri_stream_t stream);
+
+/* ---- F6: gate/up projection + SwiGLU -----------------------------------------------------
+ * w1 [2*I, K] with rows [up (I rows) | gate (I rows)]; h[m, j] = round(silu(gate_j)) * up_j.
+ * M > 8 needs workspace of lri_gateup_workspace_bytes(M, I) bytes.
+ * Replaces: FeedForward.forward's w1 / chunk / silu*mul, gpt_fast/utils.py:145-148 (and the
+ * u, g part of FuseAttentionMLP, utils.py:311-313, 385). */
+size_t lri_gateup_workspace_bytes(int64_t M, int I);
+int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t M, int I, int K,
+                      void* workspace, size_t workspace_bytes, lri_stream_t stream);
+
+/* ---- F3: GQA decode attention, split over the sequence --------------------------------------
+ * One query token per sequence.  q [B, n_head, head_dim]; caches [B_max, n_kv, smax, head_dim];
+ * context = positions 0..input_pos[0] inclusive (the new key is already in the cache); query
+ * head h reads kv head h / (n_head / n_kv); scale 1/sqrt(head_dim); out [B, n_head*head_dim].
+ * The sequence is cut into num_splits ranges handled by different CTAs and merged by the last
+ * CTA to finish, so the grid does not depend on the position.  scratch: at least
+ * lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits) bytes, 16-byte aligned;
+ * its first 32768 bytes are arrival counters that must be zero before the first call
+ * (each call leaves them zero).  Calls sharing one scratch must not overlap on the device.
+ * Replaces: the decode case of gpt_fast/utils.py:252-255 (repeat_interleave + SDPA over the
+ * whole cache under mask = causal_mask[input_pos]). */
+size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int head_dim, int num_splits);
+int lri_attn_decode(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                    const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
+                    int head_dim, int64_t smax, int num_splits, void* scratch,
+                    size_t scratch_bytes, lri_stream_t stream);
+
+/* ---- F4: causal GQA prefill attention --------------------------------------------------------
+ * q [B, S, n_head, head_dim]; query s has position input_pos[0] + s (positions must be
+ * consecutive, as in the reference's only caller, benchmark.py:138) and attends cache positions
+ * 0..input_pos[0]+s.  out [B, S, n_head*head_dim].
+ * Replaces: the prefill case of gpt_fast/utils.py:252-257. */
+int lri_attn_prefill(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                     const void* input_pos, int pos_is_i64, void* out, int B, int S, int n_head,
+                     int n_kv, int head_dim, int64_t smax, lri_stream_t stream);
+
+/* ---- F8: all-reduce over peer memory (one process per GPU) -----------------------------------
+ * A communicator owns, on every rank, one inbox buffer that all peers can write.  One-shot
+ * all-reduce: every rank stores its partial into slot `rank` of each peer's inbox, then raises
+ * a per-peer flag; the consumer waits (bounded) for all flags of the current epoch and sums
+ * the slots in fp32.  The wait gives up after `timeout_ms` and records LRI_ERR_TIMEOUT
+ * in a device status word that lri_comm_status() reads; it never traps and never spins forever.
+ *
+ * lri_comm_create: allocates the local inbox with cudaMalloc (the one allocation this library
+ *   makes; it synchronises) and returns an opaque handle plus a 64-byte IPC handle to send
+ *   to the peers.  max_elems = largest message in elements; slots are double buffered.
+ * lri_comm_connect: `ipc_handles` = world*64 bytes gathered from all ranks (host memory).
+ * lri_allreduce: in-place-capable SUM of `count` elements of `dtype`; out = sum over ranks of
+ *   their `in`.  Epochs advance from a device-resident counter, so graph replays stay correct.
+ * Replaces: all_reduce_func / dist.all_reduce, gpt_fast/utils.py:390-397. */
+typedef struct lri_comm lri_comm;
+int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm** comm_out,
+                    unsigned char ipc_handle_out[64]);
+int lri_comm_connect(lri_comm* comm, const unsigned char* ipc_handles /* host, world*64 */);
+int lri_allreduce(lri_comm* comm, int dtype, const void* in, void* out, int64_t count,
+                  int timeout_ms, lri_stream_t stream);
+/* Reads (and clears) the device status word: LRI_OK or LRI_ERR_TIMEOUT.  Synchronises `stream`. */
+int lri_comm_status(lri_comm* comm, lri_stream_t stream);
+int lri_comm_destroy(lri_comm* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LRI_B200_H_ */

@@ -1,0 +1,538 @@
+// F3: GQA decode attention split over the sequence (one query token per sequence), and
+// F4: causal GQA prefill attention (flash-attention style, tensor-core tiles via mma.sync).
+//
+// Both read the dense KV cache [B_max, n_kv, smax, head_dim] and the current position from
+// device memory, use fp32 softmax state, and round the output once to the storage type.
+#include "common.cuh"
+
+namespace lri {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// =====================================================================================================
+// F3 decode
+// =====================================================================================================
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kDecUnroll = 4;  // positions per row group and loop iteration
+
+struct DecodeParams {
+  const void* q;        // [B, n_head, HD]
+  const void* k_cache;  // [B_max, n_kv, smax, HD]
+  const void* v_cache;
+  const void* input_pos;
+  int pos_is_i64;
+  void* out;  // [B, n_head * HD]
+  int n_head, n_kv;
+  int64_t smax;
+  int num_splits;
+  float scale_log2;  // log2(e) / sqrt(HD)
+  unsigned int* counters;  // [B * n_head] (one per (batch, head tile) is used)
+  float* part_ml;          // [B, n_head, num_splits, 2]
+  float* part_o;           // [B, n_head, num_splits, HD]
+};
+
+// Grid (num_splits, n_kv * tiles_per_kv, B); a CTA handles GT query heads that share one kv head
+// over one range of positions.  LPR lanes hold one cache row (8 elements each); the 32 / LPR row
+// groups of a warp and the warps of the CTA take interleaved positions.
+template <typename T, int HD, int GT>
+__global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeParams p) {
+  constexpr int LPR = HD / 8;        // lanes per row
+  constexpr int RPW = 32 / LPR;      // row groups per warp
+  constexpr int NRG = RPW * kDecWarps;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sl = lane % LPR;         // which 8 elements of the row
+  const int rg = warp * RPW + lane / LPR;
+  const int split = blockIdx.x;
+  const int g = p.n_head / p.n_kv;
+  const int tiles_per_kv = g / GT;
+  const int kvh = blockIdx.y / tiles_per_kv;
+  const int head0 = kvh * g + (blockIdx.y % tiles_per_kv) * GT;
+  const int b = blockIdx.z;
+
+  int64_t ctx = load_pos(p.input_pos, p.pos_is_i64, 0) + 1;
+  ctx = ctx < 0 ? 0 : (ctx > p.smax ? p.smax : ctx);
+  const int64_t chunk = (ctx + p.num_splits - 1) / p.num_splits;
+  const int64_t p0 = split * chunk;
+  const int64_t p1 = (p0 + chunk < ctx) ? p0 + chunk : ctx;
+
+  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
+  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
+
+  float qf[GT][8];
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+    const T* qp = static_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.n_head + head0 + h) * HD + sl * 8;
+    unpack8<T>(*reinterpret_cast<const uint4*>(qp), qf[h]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qf[h][e] *= p.scale_log2;
+  }
+
+  float m[GT], l[GT], acc[GT][8];
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+  }
+
+  for (int64_t j0 = p0 + rg; j0 < p1; j0 += static_cast<int64_t>(NRG) * kDecUnroll) {
+    uint4 kv[kDecUnroll], vv[kDecUnroll];
+    bool valid[kDecUnroll];
+#pragma unroll
+    for (int t = 0; t < kDecUnroll; ++t) {
+      const int64_t j = j0 + static_cast<int64_t>(t) * NRG;
+      valid[t] = j < p1;
+      const int64_t jc = valid[t] ? j : p1 - 1;
+      kv[t] = ld_stream16(kbase + jc * HD);
+      vv[t] = ld_stream16(vbase + jc * HD);
+    }
+    float s[kDecUnroll][GT];
+#pragma unroll
+    for (int t = 0; t < kDecUnroll; ++t) {
+      float kf[8];
+      unpack8<T>(kv[t], kf);
+#pragma unroll
+      for (int h = 0; h < GT; ++h) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(qf[h][e], kf[e], d);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        s[t][h] = valid[t] ? d : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < GT; ++h) {
+      float mx = s[0][h];
+#pragma unroll
+      for (int t = 1; t < kDecUnroll; ++t) mx = fmaxf(mx, s[t][h]);
+      const float m_new = fmaxf(m[h], mx);  // finite: position j0 is valid
+      const float corr = exp2f(m[h] - m_new);
+      l[h] *= corr;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
+      m[h] = m_new;
+#pragma unroll
+      for (int t = 0; t < kDecUnroll; ++t) s[t][h] = exp2f(s[t][h] - m_new);
+    }
+#pragma unroll
+    for (int t = 0; t < kDecUnroll; ++t) {
+      float vf[8];
+      unpack8<T>(vv[t], vf);
+#pragma unroll
+      for (int h = 0; h < GT; ++h) {
+        l[h] += s[t][h];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(s[t][h], vf[e], acc[h][e]);
+      }
+    }
+  }
+
+  // ---- merge the row groups of the CTA ---------------------------------------------------------
+  __shared__ float sm_m[NRG][GT];
+  __shared__ float sm_l[NRG][GT];
+  __shared__ float sm_o[NRG][GT][HD];
+  __shared__ unsigned int ticket_s;
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+    if (sl == 0) {
+      sm_m[rg][h] = m[h];
+      sm_l[rg][h] = l[h];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sm_o[rg][h][sl * 8 + e] = acc[h][e];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < GT * HD; idx += kDecThreads) {
+    const int h = idx / HD, e = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < NRG; ++r) mm = fmaxf(mm, sm_m[r][h]);
+    float ll = 0.f, oo = 0.f;
+    if (mm > -INFINITY) {
+#pragma unroll
+      for (int r = 0; r < NRG; ++r) {
+        const float w = exp2f(sm_m[r][h] - mm);  // 0 for groups that saw no position
+        ll += sm_l[r][h] * w;
+        oo += sm_o[r][h][e] * w;
+      }
+    }
+    const int64_t slot = (static_cast<int64_t>(b) * p.n_head + head0 + h) * p.num_splits + split;
+    p.part_o[slot * HD + e] = oo;
+    if (e == 0) {
+      p.part_ml[slot * 2] = mm;
+      p.part_ml[slot * 2 + 1] = ll;
+    }
+  }
+
+  // ---- the last CTA of this (batch, head tile) merges the splits ---------------------------------
+  __threadfence();
+  __syncthreads();
+  unsigned int* counter = p.counters + static_cast<int64_t>(b) * gridDim.y + blockIdx.y;
+  if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1u);
+  __syncthreads();
+  if (ticket_s != static_cast<unsigned int>(p.num_splits - 1)) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < GT * HD; idx += kDecThreads) {
+    const int h = idx / HD, e = idx % HD;
+    const int64_t slot0 = (static_cast<int64_t>(b) * p.n_head + head0 + h) * p.num_splits;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < p.num_splits; ++sp) mm = fmaxf(mm, __ldcg(p.part_ml + (slot0 + sp) * 2));
+    float ll = 0.f, oo = 0.f;
+    if (mm > -INFINITY) {
+      for (int sp = 0; sp < p.num_splits; ++sp) {
+        const float w = exp2f(__ldcg(p.part_ml + (slot0 + sp) * 2) - mm);
+        ll += __ldcg(p.part_ml + (slot0 + sp) * 2 + 1) * w;
+        oo += __ldcg(p.part_o + (slot0 + sp) * HD + e) * w;
+      }
+    }
+    const float r = ll > 0.f ? oo / ll : 0.f;
+    static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.n_head + head0 + h) * HD + e] = Num<T>::from_f(r);
+  }
+  if (threadIdx.x == 0) *counter = 0u;  // ready for the next call
+}
+
+// =====================================================================================================
+// F4 prefill
+// =====================================================================================================
+constexpr int kPfBlockM = 64, kPfBlockN = 64, kPfThreads = 128;
+
+struct PrefillParams {
+  const void* q;  // [B, S, n_head, HD]
+  const void* k_cache;
+  const void* v_cache;
+  const void* input_pos;
+  int pos_is_i64;
+  void* out;  // [B, S, n_head * HD]
+  int S, n_head, n_kv;
+  int64_t smax;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // src-size 0 zero-fills the 16 destination bytes
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Grid (ceil(S / 64), n_head, B).  Each of the 4 warps owns 16 query rows; K and V tiles of 64
+// positions are staged in shared memory with padded rows (HD + 8 elements) so that ldmatrix
+// reads are bank-conflict free.
+template <typename T, int HD>
+__global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const PrefillParams p) {
+  constexpr int LDS = HD + 8;          // padded row length in elements
+  constexpr int KB = HD / 16;          // k blocks of the QK^T product
+  constexpr int NB = kPfBlockN / 8;    // n blocks (key columns) of a score tile
+  constexpr int OB = HD / 8;           // n blocks of the output
+  constexpr int CPR = HD / 8;          // 16-byte chunks per row
+  extern __shared__ __align__(16) uint8_t pf_smem[];
+  T* sq = reinterpret_cast<T*>(pf_smem);
+  T* sk = sq + kPfBlockM * LDS;
+  T* sv = sk + kPfBlockN * LDS;
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q0 = blockIdx.x * kPfBlockM;
+  const int head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int kvh = head / (p.n_head / p.n_kv);
+  int64_t pos0 = load_pos(p.input_pos, p.pos_is_i64, 0);
+  pos0 = pos0 < 0 ? 0 : pos0;
+  const int q_end = (q0 + kPfBlockM < p.S) ? q0 + kPfBlockM : p.S;
+  int64_t kv_end = pos0 + q_end;  // keys 0 .. pos0 + q_end - 1 are visible to the last row
+  kv_end = kv_end > p.smax ? p.smax : kv_end;
+
+  const T* qg = static_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.S * p.n_head + head) * HD;
+  const T* kg = static_cast<const T*>(p.k_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD;
+  const T* vg = static_cast<const T*>(p.v_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD;
+
+  // ---- Q tile -> shared -> A fragments ---------------------------------------------------------------
+  for (int c = threadIdx.x; c < kPfBlockM * CPR; c += kPfThreads) {
+    const int r = c / CPR, cc = c % CPR;
+    const int s = q0 + r;
+    const bool ok = s < p.S;
+    const T* src = qg + static_cast<int64_t>(ok ? s : 0) * p.n_head * HD + cc * 8;
+    cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(sq + r * LDS + cc * 8)), src, ok);
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  uint32_t qa[KB][4];
+  {
+    const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int col = (lane >> 4) * 8;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb)
+      ldmatrix_x4(static_cast<uint32_t>(__cvta_generic_to_shared(sq + row * LDS + kb * 16 + col)), qa[kb]);
+  }
+
+  float o[OB][4];
+#pragma unroll
+  for (int i = 0; i < OB; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // absolute positions of the two query rows this thread holds scores for
+  const int64_t qpos0 = pos0 + q0 + warp * 16 + (lane >> 2);
+  const int64_t qpos1 = qpos0 + 8;
+
+  const int n_tiles = static_cast<int>((kv_end + kPfBlockN - 1) / kPfBlockN);
+  for (int t = 0; t < n_tiles; ++t) {
+    const int64_t kv0 = static_cast<int64_t>(t) * kPfBlockN;
+    __syncthreads();  // everyone is done with the previous K/V tiles
+    for (int c = threadIdx.x; c < kPfBlockN * CPR; c += kPfThreads) {
+      const int r = c / CPR, cc = c % CPR;
+      const int64_t j = kv0 + r;
+      const bool ok = j < kv_end;
+      const int64_t jc = ok ? j : 0;
+      cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(sk + r * LDS + cc * 8)), kg + jc * HD + cc * 8, ok);
+      cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(sv + r * LDS + cc * 8)), vg + jc * HD + cc * 8, ok);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    // ---- scores: 16 x 64 per warp ------------------------------------------------------------------
+    float sc[NB][4];
+#pragma unroll
+    for (int i = 0; i < NB; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[i][e] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+      for (int nb2 = 0; nb2 < NB / 2; ++nb2) {
+        // two key blocks (16 keys) x 16 k-elements per ldmatrix.x4
+        const int krow = nb2 * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int kcol = kb * 16 + ((lane >> 3) & 1) * 8;
+        uint32_t bf[4];
+        ldmatrix_x4(static_cast<uint32_t>(__cvta_generic_to_shared(sk + krow * LDS + kcol)), bf);
+        mma16816<T>(sc[2 * nb2], qa[kb], bf[0], bf[1]);
+        mma16816<T>(sc[2 * nb2 + 1], qa[kb], bf[2], bf[3]);
+      }
+    }
+
+    // ---- scale, causal mask, online softmax -----------------------------------------------------------
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int64_t key = kv0 + nb * 8 + (lane & 3) * 2;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t kj = key + (e & 1);
+        const int64_t qp = (e < 2) ? qpos0 : qpos1;
+        const float v = (kj <= qp && kj < kv_end) ? sc[nb][e] * p.scale_log2 : -INFINITY;
+        sc[nb][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      // a row with no visible key yet keeps m = -inf; use 0 as the reference so exp2 stays finite
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = exp2f(m_run[r] - m_use);
+      m_run[r] = m_new;
+      mx[r] = m_use;
+      l_run[r] *= corr[r];
+    }
+    uint32_t pa[NB / 2][4];
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pv[e] = exp2f(sc[nb][e] - mx[e >> 1]);
+        rs[e >> 1] += pv[e];
+      }
+      pa[nb >> 1][(nb & 1) * 2 + 0] = pack2<T>(pv[0], pv[1]);
+      pa[nb >> 1][(nb & 1) * 2 + 1] = pack2<T>(pv[2], pv[3]);
+    }
+    l_run[0] += rs[0];
+    l_run[1] += rs[1];
+#pragma unroll
+    for (int i = 0; i < OB; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+
+    // ---- O += P V ----------------------------------------------------------------------------------------
+#pragma unroll
+    for (int jb = 0; jb < kPfBlockN / 16; ++jb) {
+#pragma unroll
+      for (int ob2 = 0; ob2 < OB / 2; ++ob2) {
+        const int vrow = jb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int vcol = ob2 * 16 + (lane >> 4) * 8;
+        uint32_t bf[4];
+        ldmatrix_x4_trans(static_cast<uint32_t>(__cvta_generic_to_shared(sv + vrow * LDS + vcol)), bf);
+        mma16816<T>(o[2 * ob2], pa[jb], bf[0], bf[1]);
+        mma16816<T>(o[2 * ob2 + 1], pa[jb], bf[2], bf[3]);
+      }
+    }
+  }
+
+  // ---- finalize: row sums across the 4 lanes of a row, normalise, store ---------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
+  const float inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  const int s0 = q0 + warp * 16 + (lane >> 2), s1 = s0 + 8;
+  T* og = static_cast<T*>(p.out) + (static_cast<int64_t>(b) * p.S * p.n_head + head) * HD;
+#pragma unroll
+  for (int i = 0; i < OB; ++i) {
+    const int e = i * 8 + (lane & 3) * 2;
+    if (s0 < p.S)
+      *reinterpret_cast<uint32_t*>(og + static_cast<int64_t>(s0) * p.n_head * HD + e) = pack2<T>(o[i][0] * inv0, o[i][1] * inv0);
+    if (s1 < p.S)
+      *reinterpret_cast<uint32_t*>(og + static_cast<int64_t>(s1) * p.n_head * HD + e) = pack2<T>(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+template <typename T, int HD>
+int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
+  const int g = p.n_head / p.n_kv;
+  const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
+  dim3 grid(p.num_splits, p.n_kv * (g / gt), B);
+  if (gt == 4)
+    attn_decode_kernel<T, HD, 4><<<grid, kDecThreads, 0, st>>>(p);
+  else if (gt == 2)
+    attn_decode_kernel<T, HD, 2><<<grid, kDecThreads, 0, st>>>(p);
+  else
+    attn_decode_kernel<T, HD, 1><<<grid, kDecThreads, 0, st>>>(p);
+  LRI_LAUNCH_CHECK("attn_decode_kernel");
+  return LRI_OK;
+}
+
+template <typename T, int HD>
+int launch_prefill(const PrefillParams& p, int B, cudaStream_t st) {
+  constexpr int smem = (kPfBlockM + 2 * kPfBlockN) * (HD + 8) * 2;
+  auto kern = attn_prefill_kernel<T, HD>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  dim3 grid((p.S + kPfBlockM - 1) / kPfBlockM, p.n_head, B);
+  kern<<<grid, kPfThreads, smem, st>>>(p);
+  LRI_LAUNCH_CHECK("attn_prefill_kernel");
+  return LRI_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+// The arrival counters take a fixed region at the start of the scratch buffer, so that calls
+// with different batch sizes can share one zero-initialised buffer.
+constexpr size_t kCounterBytes = 32768;
+constexpr size_t kMaxCounterRows = kCounterBytes / 4;
+
+int check_attn(const char* who, int dtype, int B, int n_head, int n_kv, int head_dim, int64_t smax) {
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "%s: dtype %d", who, dtype);
+  LRI_REQUIRE(B >= 0 && B <= 65535, LRI_ERR_ARG, "%s: B=%d", who, B);
+  LRI_REQUIRE(n_head > 0 && n_kv > 0 && n_head % n_kv == 0 && n_head <= 65535, LRI_ERR_ARG,
+              "%s: n_head=%d must be a positive multiple of n_kv=%d", who, n_head, n_kv);
+  LRI_REQUIRE(head_dim == 64 || head_dim == 128, LRI_ERR_UNSUPPORTED, "%s: head_dim=%d (64 and 128 are built)", who,
+              head_dim);
+  LRI_REQUIRE(smax > 0, LRI_ERR_ARG, "%s: smax=%lld", who, (long long)smax);
+  return LRI_OK;
+}
+
+}  // namespace
+}  // namespace lri
+
+using namespace lri;
+
+extern "C" size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int head_dim, int num_splits) {
+  (void)n_kv;
+  if (B <= 0 || n_head <= 0 || head_dim <= 0 || num_splits <= 0) return 0;
+  const size_t rows = static_cast<size_t>(B) * n_head;
+  return kCounterBytes + align_up(rows * num_splits * 2 * 4, 16) + rows * num_splits * head_dim * 4;
+}
+
+extern "C" int lri_attn_decode(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                               const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
+                               int head_dim, int64_t smax, int num_splits, void* scratch, size_t scratch_bytes,
+                               lri_stream_t stream) {
+  int rc = check_attn("attn_decode", dtype, B, n_head, n_kv, head_dim, smax);
+  if (rc != LRI_OK) return rc;
+  LRI_REQUIRE(q && k_cache && v_cache && input_pos && out, LRI_ERR_ARG, "attn_decode: NULL pointer");
+  LRI_REQUIRE(num_splits >= 1 && num_splits <= 1024, LRI_ERR_ARG, "attn_decode: num_splits=%d", num_splits);
+  LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
+              "attn_decode: pointers must be 16-byte aligned");
+  LRI_REQUIRE(scratch && aligned16(scratch) &&
+                  scratch_bytes >= lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits),
+              LRI_ERR_WORKSPACE, "attn_decode: scratch of %zu bytes (16-byte aligned) required",
+              lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits));
+  if (B == 0) return LRI_OK;
+  const size_t rows = static_cast<size_t>(B) * n_head;
+  LRI_REQUIRE(rows <= kMaxCounterRows, LRI_ERR_UNSUPPORTED, "attn_decode: B*n_head=%zu exceeds %zu", rows,
+              kMaxCounterRows);
+  DecodeParams p{};
+  p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64, p.out = out;
+  p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.num_splits = num_splits;
+  p.scale_log2 = kLog2e / sqrtf(static_cast<float>(head_dim));
+  uint8_t* s = static_cast<uint8_t*>(scratch);
+  p.counters = reinterpret_cast<unsigned int*>(s);
+  p.part_ml = reinterpret_cast<float*>(s + kCounterBytes);
+  p.part_o = reinterpret_cast<float*>(s + kCounterBytes + align_up(rows * num_splits * 2 * 4, 16));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == LRI_BF16)
+    return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(p, B, st) : launch_decode<__nv_bfloat16, 64>(p, B, st);
+  return head_dim == 128 ? launch_decode<__half, 128>(p, B, st) : launch_decode<__half, 64>(p, B, st);
+}
+
+extern "C" int lri_attn_prefill(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                                const void* input_pos, int pos_is_i64, void* out, int B, int S, int n_head, int n_kv,
+                                int head_dim, int64_t smax, lri_stream_t stream) {
+  int rc = check_attn("attn_prefill", dtype, B, n_head, n_kv, head_dim, smax);
+  if (rc != LRI_OK) return rc;
+  LRI_REQUIRE(q && k_cache && v_cache && input_pos && out, LRI_ERR_ARG, "attn_prefill: NULL pointer");
+  LRI_REQUIRE(S >= 0 && S <= (1 << 22), LRI_ERR_ARG, "attn_prefill: S=%d", S);
+  LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
+              "attn_prefill: pointers must be 16-byte aligned");
+  if (B == 0 || S == 0) return LRI_OK;
+  PrefillParams p{};
+  p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64, p.out = out;
+  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax;
+  p.scale_log2 = kLog2e / sqrtf(static_cast<float>(head_dim));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == LRI_BF16)
+    return head_dim == 128 ? launch_prefill<__nv_bfloat16, 128>(p, B, st) : launch_prefill<__nv_bfloat16, 64>(p, B, st);
+  return head_dim == 128 ? launch_prefill<__half, 128>(p, B, st) : launch_prefill<__half, 64>(p, B, st);
+}

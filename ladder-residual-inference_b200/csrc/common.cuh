@@ -1,0 +1,146 @@
+// Shared device/host helpers for the sm_100a kernels: dtype traits, 16-byte vector access,
+// error reporting of the C ABI, launch counting.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lri_b200.h"
+
+namespace lri {
+
+// ---- host side ---------------------------------------------------------------------------
+// Formats the calling thread's error message and returns `code`.
+int fail(int code, const char* fmt, ...);
+void count_launch(int n = 1);
+
+#define LRI_REQUIRE(cond, code, ...)                  \
+  do {                                                \
+    if (!(cond)) return ::lri::fail(code, __VA_ARGS__); \
+  } while (0)
+
+#define LRI_CUDA(expr)                                                                        \
+  do {                                                                                        \
+    cudaError_t e_ = (expr);                                                                  \
+    if (e_ != cudaSuccess)                                                                    \
+      return ::lri::fail(LRI_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                         __FILE__, __LINE__);                                                 \
+  } while (0)
+
+// After a kernel launch: reports a launch-configuration error without synchronising.
+#define LRI_LAUNCH_CHECK(what)                                                                 \
+  do {                                                                                         \
+    cudaError_t e_ = cudaPeekAtLastError();                                                    \
+    if (e_ != cudaSuccess) {                                                                   \
+      cudaGetLastError();                                                                      \
+      return ::lri::fail(LRI_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e_)); \
+    }                                                                                          \
+    ::lri::count_launch();                                                                     \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- dtype traits ------------------------------------------------------------------------
+template <typename T>
+struct Num;
+
+template <>
+struct Num<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float f) { return __float2bfloat16_rn(f); }
+  // two packed elements (low half first) to two floats
+  static __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi) {
+    lo = __uint_as_float(u << 16);
+    hi = __uint_as_float(u & 0xffff0000u);
+  }
+};
+
+template <>
+struct Num<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float f) { return __float2half_rn(f); }
+  static __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi) {
+    __half2 h = *reinterpret_cast<__half2*>(&u);
+    float2 f = __half22float2(h);
+    lo = f.x;
+    hi = f.y;
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  Num<T>::unpack2(v.x, f[0], f[1]);
+  Num<T>::unpack2(v.y, f[2], f[3]);
+  Num<T>::unpack2(v.z, f[4], f[5]);
+  Num<T>::unpack2(v.w, f[6], f[7]);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  T a = Num<T>::from_f(lo), b = Num<T>::from_f(hi);
+  uint16_t ua = *reinterpret_cast<uint16_t*>(&a), ub = *reinterpret_cast<uint16_t*>(&b);
+  return static_cast<uint32_t>(ua) | (static_cast<uint32_t>(ub) << 16);
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  v.x = pack2<T>(f[0], f[1]);
+  v.y = pack2<T>(f[2], f[3]);
+  v.z = pack2<T>(f[4], f[5]);
+  v.w = pack2<T>(f[6], f[7]);
+  return v;
+}
+
+// round-trip through the storage type: the value an op's output has after it is stored
+template <typename T>
+__device__ __forceinline__ float rnd(float f) {
+  return Num<T>::to_f(Num<T>::from_f(f));
+}
+
+// 16-byte streaming load that does not allocate in L1 (weights are read exactly once)
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ int64_t load_pos(const void* input_pos, int pos_is_i64, int64_t i) {
+  return pos_is_i64 ? reinterpret_cast<const int64_t*>(input_pos)[i]
+                    : static_cast<int64_t>(reinterpret_cast<const int32_t*>(input_pos)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// SiLU as torch evaluates it in fp32: x / (1 + exp(-x))
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// silu(gate) rounded to T, times up (both already rounded to T), rounded to T.
+template <typename T>
+__device__ __forceinline__ T swiglu_rounded(float up_rounded, float gate_rounded) {
+  float s = rnd<T>(silu_f(gate_rounded));
+  return Num<T>::from_f(s * up_rounded);
+}
+
+// Rotation of one adjacent pair in fp32 with separately rounded products (no FMA
+// contraction), from values and table entries already rounded to T.
+__device__ __forceinline__ void rope_pair(float x0, float x1, float c, float s, float& o0, float& o1) {
+  o0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+  o1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+}
+
+}  // namespace lri

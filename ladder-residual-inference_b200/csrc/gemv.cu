@@ -1,0 +1,159 @@
+// Weight-streaming GEMV family for small-batch decode (M <= 8 token rows).
+//
+// y[m, n] = sum_k x[m, k] * W[n, k], W row-major [N, K] (the nn.Linear layout, K contiguous).
+// The kernel is HBM-bound: every weight byte is read exactly once with 16-byte streaming
+// loads that bypass L1, and a thread keeps R*U such loads in flight.  A CTA owns R weight
+// rows; its warps split K in interleaved 256-element chunks, reduce with shuffles and then
+// through shared memory; the few threads holding the final sums run the fused epilogue:
+//   PLAIN   store (optionally + addend)                       wo / w2 / LM head
+//   SWIGLU  rows (j, I + j) -> silu(gate) * up                 w1
+//   QKV     rotate adjacent pairs, scatter q / k-cache / v-cache   wqkv
+#include "linear.cuh"
+
+namespace lri {
+namespace {
+
+constexpr int kGemvMaxWarps = 8;
+
+template <typename T, int M, int R, int U, int EPI>
+__global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearParams p) {
+  static_assert(R % 2 == 0, "epilogues work on pairs of rows");
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int W = blockDim.x >> 5;
+  const int K = p.k;
+  const T* __restrict__ w = static_cast<const T*>(p.w);
+  const T* __restrict__ x = static_cast<const T*>(p.x);
+
+  // weight rows of this CTA (clamped: rows past the end recompute the last row and are not stored)
+  const T* wrow[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    int64_t row;
+    if (EPI == EPI_SWIGLU) {
+      int64_t j = static_cast<int64_t>(blockIdx.x) * (R / 2) + (r >> 1);
+      j = j < p.n ? j : p.n - 1;
+      row = (r & 1) ? p.n + j : j;  // even slot: up row j, odd slot: gate row I + j
+    } else {
+      row = static_cast<int64_t>(blockIdx.x) * R + r;
+      row = row < p.n ? row : p.n - 1;
+    }
+    wrow[r] = w + row * K;
+  }
+  const T* xrow[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) xrow[m] = x + static_cast<int64_t>(m < p.m ? m : p.m - 1) * K;
+
+  float acc[M][R];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
+
+  const int nchunks = (K + 255) >> 8;
+  for (int c0 = warp; c0 < nchunks; c0 += W * U) {
+    uint4 wv[U][R];
+    uint4 xv[U][M];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = ((c0 + u * W) << 8) + lane * 8;
+      const bool ok = k < K;
+#pragma unroll
+      for (int r = 0; r < R; ++r) wv[u][r] = ok ? ld_stream16(wrow[r] + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+        xv[u][m] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow[m] + k)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float xf[M][8];
+#pragma unroll
+      for (int m = 0; m < M; ++m) unpack8<T>(xv[u][m], xf[m]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float wf[8];
+        unpack8<T>(wv[u][r], wf);
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[m][r] = fmaf(wf[e], xf[m][e], acc[m][r]);
+      }
+    }
+  }
+
+  __shared__ float red[kGemvMaxWarps][M * R];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float s = warp_sum(acc[m][r]);
+      if (lane == 0) red[warp][m * R + r] = s;
+    }
+  __syncthreads();
+
+  if (threadIdx.x >= M * (R / 2)) return;
+  const int m = threadIdx.x / (R / 2);
+  const int j = threadIdx.x % (R / 2);
+  if (m >= p.m) return;
+  float s0 = 0.f, s1 = 0.f;
+  for (int wi = 0; wi < W; ++wi) {
+    s0 += red[wi][m * R + 2 * j];
+    s1 += red[wi][m * R + 2 * j + 1];
+  }
+  // the projection's own rounding to the storage type (nn.Linear output)
+  const float v0 = rnd<T>(s0), v1 = rnd<T>(s1);
+
+  if (EPI == EPI_PLAIN) {
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * R + 2 * j;
+    T* y = static_cast<T*>(p.y) + static_cast<int64_t>(m) * p.n;
+    const T* add = p.addend ? static_cast<const T*>(p.addend) + static_cast<int64_t>(m) * p.n : nullptr;
+    if (n < p.n) y[n] = Num<T>::from_f(add ? v0 + Num<T>::to_f(add[n]) : v0);
+    if (n + 1 < p.n) y[n + 1] = Num<T>::from_f(add ? v1 + Num<T>::to_f(add[n + 1]) : v1);
+  } else if (EPI == EPI_SWIGLU) {
+    const int64_t jj = static_cast<int64_t>(blockIdx.x) * (R / 2) + j;
+    if (jj < p.n) static_cast<T*>(p.y)[static_cast<int64_t>(m) * p.n + jj] = swiglu_rounded<T>(v0, v1);
+  } else {
+    const int64_t n = static_cast<int64_t>(blockIdx.x) * R + 2 * j;  // even
+    if (n >= p.n) return;
+    qkv_epilogue_pair<T>(p, m, n, v0, v1);
+  }
+}
+
+template <typename T, int M, int U, int EPI>
+int launch_gemv(const LinearParams& p, cudaStream_t st) {
+  constexpr int R = 4;
+  const int nchunks = (p.k + 255) >> 8;
+  int W = (nchunks + U - 1) / U;
+  W = W < 1 ? 1 : (W > kGemvMaxWarps ? kGemvMaxWarps : W);
+  const int64_t per_cta = EPI == EPI_SWIGLU ? R / 2 : R;
+  const int64_t grid = (p.n + per_cta - 1) / per_cta;
+  gemv_kernel<T, M, R, U, EPI><<<static_cast<unsigned>(grid), W * 32, 0, st>>>(p);
+  LRI_LAUNCH_CHECK("gemv_kernel");
+  return LRI_OK;
+}
+
+template <typename T, int EPI>
+int dispatch_m(const LinearParams& p, cudaStream_t st) {
+  if (p.m <= 1) return launch_gemv<T, 1, 4, EPI>(p, st);
+  if (p.m <= 2) return launch_gemv<T, 2, 4, EPI>(p, st);
+  if (p.m <= 4) return launch_gemv<T, 4, 2, EPI>(p, st);
+  return launch_gemv<T, 8, 1, EPI>(p, st);
+}
+
+template <typename T>
+int dispatch_epi(int epi, const LinearParams& p, cudaStream_t st) {
+  switch (epi) {
+    case EPI_PLAIN: return dispatch_m<T, EPI_PLAIN>(p, st);
+    case EPI_SWIGLU: return dispatch_m<T, EPI_SWIGLU>(p, st);
+    default: return dispatch_m<T, EPI_QKV>(p, st);
+  }
+}
+
+}  // namespace
+
+int gemv_launch(int dtype, int epi, const LinearParams& p, cudaStream_t st) {
+  if (p.m < 1 || p.m > kGemvMaxRows) return fail(LRI_ERR_ARG, "gemv: m=%d outside 1..%d", p.m, kGemvMaxRows);
+  return dtype == LRI_BF16 ? dispatch_epi<__nv_bfloat16>(epi, p, st) : dispatch_epi<__half>(epi, p, st);
+}
+
+}  // namespace lri

@@ -1,0 +1,301 @@
+// C entry points of the linear-layer family (F2, F5, F6, F7): argument checks, the choice
+// between the decode GEMV and the prefill GEMM, the elementwise epilogues that follow the
+// GEMM (RoPE + cache scatter, SwiGLU, addend), and a plain SIMT GEMM kept as a selectable
+// back end for shapes the tcgen05 kernel does not take.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "linear.cuh"
+
+namespace lri {
+
+bool gemm_tcgen05_supports(int64_t m, int n, int k);
+int gemm_tcgen05_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);
+int gemm_tcgen05_status_read_and_clear(int* status_out);
+
+// ---- error text, launch counter, back-end switch ----------------------------------------------
+namespace {
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+// LRI_GEMM_BACKEND=simt|tcgen05 in the environment sets the initial choice (debugging aid).
+int backend_from_env() {
+  const char* e = getenv("LRI_GEMM_BACKEND");
+  if (e && strcmp(e, "simt") == 0) return LRI_GEMM_SIMT;
+  if (e && strcmp(e, "tcgen05") == 0) return LRI_GEMM_TCGEN05;
+  return LRI_GEMM_AUTO;
+}
+std::atomic<int> g_backend{backend_from_env()};
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int current_gemm_backend() { return g_backend.load(); }
+
+namespace {
+
+// ---- SIMT GEMM: 64x64 tile, 256 threads, 4x4 outputs per thread, fp32 accumulation --------------
+constexpr int kST = 64, kSK = 32, kSLd = kST + 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ w,
+                                                        T* __restrict__ c, int m, int n, int k) {
+  __shared__ float as[kSK][kSLd];
+  __shared__ float ws[kSK][kSLd];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kST, n0 = static_cast<int64_t>(blockIdx.x) * kST;
+  const int lrow = tid >> 2, lk = (tid & 3) * 8;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < k; k0 += kSK) {
+    float fa[8] = {}, fw[8] = {};
+    if (m0 + lrow < m && k0 + lk < k) unpack8<T>(*reinterpret_cast<const uint4*>(a + (m0 + lrow) * k + k0 + lk), fa);
+    if (n0 + lrow < n && k0 + lk < k) unpack8<T>(*reinterpret_cast<const uint4*>(w + (n0 + lrow) * k + k0 + lk), fw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      as[lk + e][lrow] = fa[e];
+      ws[lk + e][lrow] = fw[e];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kSK; ++kk) {
+      const float4 av = *reinterpret_cast<const float4*>(&as[kk][ty * 4]);
+      const float4 wv = *reinterpret_cast<const float4*>(&ws[kk][tx * 4]);
+      const float ar[4] = {av.x, av.y, av.z, av.w}, wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t r = m0 + ty * 4 + i, col = n0 + tx * 4 + j;
+      if (r < m && col < n) c[r * n + col] = Num<T>::from_f(acc[i][j]);
+    }
+}
+
+template <typename T>
+int launch_simt(const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>((n + kST - 1) / kST), static_cast<unsigned>((m + kST - 1) / kST));
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(w), static_cast<T*>(c),
+                                            static_cast<int>(m), n, k);
+  LRI_LAUNCH_CHECK("gemm_simt_kernel");
+  return LRI_OK;
+}
+
+// ---- elementwise epilogues after the GEMM -----------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const T* __restrict__ ug, T* __restrict__ h, int64_t m,
+                                                          int n) {
+  // one thread per 8 outputs; ug row = [up (n) | gate (n)]
+  const int64_t vec_per_row = n >> 3;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= m * vec_per_row) return;
+  const int64_t row = i / vec_per_row, v = i - row * vec_per_row;
+  const uint4* src = reinterpret_cast<const uint4*>(ug + row * 2 * n);
+  float u[8], g[8], o[8];
+  unpack8<T>(src[v], u);
+  unpack8<T>(src[vec_per_row + v], g);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = rnd<T>(silu_f(g[e])) * u[e];
+  reinterpret_cast<uint4*>(h + row * n)[v] = pack8<T>(o);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_scatter_kernel(const T* __restrict__ qkv, const LinearParams p) {
+  // one thread per adjacent pair of the projection output
+  const int64_t width = static_cast<int64_t>(p.n_head + 2 * p.n_kv) * p.head_dim;
+  const int64_t pairs_per_row = width >> 1;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<int64_t>(p.m) * pairs_per_row) return;
+  const int64_t row = i / pairs_per_row, n = (i - row * pairs_per_row) * 2;
+  float v0, v1;
+  Num<T>::unpack2(*reinterpret_cast<const uint32_t*>(qkv + row * width + n), v0, v1);
+  qkv_epilogue_pair<T>(p, row, n, v0, v1);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) add_rows_kernel(T* __restrict__ y, const T* __restrict__ addend,
+                                                       int64_t nvec) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  float a[8], b[8];
+  unpack8<T>(reinterpret_cast<const uint4*>(y)[i], a);
+  unpack8<T>(reinterpret_cast<const uint4*>(addend)[i], b);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] += b[e];
+  reinterpret_cast<uint4*>(y)[i] = pack8<T>(a);
+}
+
+unsigned blocks_for(int64_t items, int threads) { return static_cast<unsigned>((items + threads - 1) / threads); }
+
+}  // namespace
+
+int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
+  const int backend = current_gemm_backend();
+  const bool tc_ok = gemm_tcgen05_supports(m, n, k) && aligned16(a) && aligned16(w) && aligned16(c);
+  if (backend == LRI_GEMM_TCGEN05 && !tc_ok)
+    return fail(LRI_ERR_UNSUPPORTED, "gemm: tcgen05 back end needs n %% 8 == 0, k %% 8 == 0 and 16-byte aligned pointers");
+  if (backend != LRI_GEMM_SIMT && tc_ok) return gemm_tcgen05_launch(dtype, a, w, c, m, n, k, st);
+  return dtype == LRI_BF16 ? launch_simt<__nv_bfloat16>(a, w, c, m, n, k, st)
+                           : launch_simt<__half>(a, w, c, m, n, k, st);
+}
+
+int swiglu_rows_launch(int dtype, const void* ug, void* h, int64_t m, int n, cudaStream_t st) {
+  const int64_t items = m * (n >> 3);
+  if (dtype == LRI_BF16)
+    swiglu_rows_kernel<__nv_bfloat16><<<blocks_for(items, 256), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(ug), static_cast<__nv_bfloat16*>(h), m, n);
+  else
+    swiglu_rows_kernel<__half><<<blocks_for(items, 256), 256, 0, st>>>(static_cast<const __half*>(ug),
+                                                                        static_cast<__half*>(h), m, n);
+  LRI_LAUNCH_CHECK("swiglu_rows_kernel");
+  return LRI_OK;
+}
+
+int qkv_scatter_launch(int dtype, const void* qkv, const LinearParams& p, cudaStream_t st) {
+  const int64_t items = static_cast<int64_t>(p.m) * ((static_cast<int64_t>(p.n_head + 2 * p.n_kv) * p.head_dim) >> 1);
+  if (dtype == LRI_BF16)
+    qkv_scatter_kernel<__nv_bfloat16><<<blocks_for(items, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(qkv), p);
+  else
+    qkv_scatter_kernel<__half><<<blocks_for(items, 256), 256, 0, st>>>(static_cast<const __half*>(qkv), p);
+  LRI_LAUNCH_CHECK("qkv_scatter_kernel");
+  return LRI_OK;
+}
+
+int add_rows_launch(int dtype, void* y, const void* addend, int64_t count, cudaStream_t st) {
+  const int64_t nvec = count >> 3;
+  if (dtype == LRI_BF16)
+    add_rows_kernel<__nv_bfloat16><<<blocks_for(nvec, 256), 256, 0, st>>>(
+        static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(addend), nvec);
+  else
+    add_rows_kernel<__half><<<blocks_for(nvec, 256), 256, 0, st>>>(static_cast<__half*>(y),
+                                                                    static_cast<const __half*>(addend), nvec);
+  LRI_LAUNCH_CHECK("add_rows_kernel");
+  return LRI_OK;
+}
+
+}  // namespace lri
+
+// ---- C ABI ----------------------------------------------------------------------------------------
+using namespace lri;
+
+extern "C" const char* lri_last_error(void) { return g_err; }
+extern "C" int lri_version(void) { return 100; }
+extern "C" int64_t lri_launch_count(void) { return g_launches.load(); }
+extern "C" int lri_set_gemm_backend(int backend) {
+  LRI_REQUIRE(backend >= LRI_GEMM_AUTO && backend <= LRI_GEMM_SIMT, LRI_ERR_ARG, "set_gemm_backend: %d", backend);
+  g_backend.store(backend);
+  return LRI_OK;
+}
+extern "C" int lri_gemm_status(void) {
+  int v = 0;
+  int rc = gemm_tcgen05_status_read_and_clear(&v);
+  if (rc != LRI_OK) return rc;
+  if (v != 0) return fail(LRI_ERR_TIMEOUT, "tcgen05 GEMM: a bounded mbarrier wait gave up (site %d)", v);
+  return LRI_OK;
+}
+
+static int check_common(const char* who, int dtype, const void* x, const void* w, int64_t M, int K) {
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "%s: dtype %d", who, dtype);
+  LRI_REQUIRE(x && w, LRI_ERR_ARG, "%s: NULL input", who);
+  LRI_REQUIRE(M >= 0 && M < (1ll << 31), LRI_ERR_ARG, "%s: M=%lld", who, (long long)M);
+  LRI_REQUIRE(K > 0 && K % 8 == 0, LRI_ERR_UNSUPPORTED, "%s: K=%d must be a positive multiple of 8", who, K);
+  LRI_REQUIRE(aligned16(x) && aligned16(w), LRI_ERR_ALIGN, "%s: x and w must be 16-byte aligned", who);
+  return LRI_OK;
+}
+
+extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M, int N,
+                          int K, void* workspace, size_t workspace_bytes, lri_stream_t stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_common("linear", dtype, x, w, M, K);
+  if (rc != LRI_OK) return rc;
+  LRI_REQUIRE(y != nullptr && N > 0, LRI_ERR_ARG, "linear: y is NULL or N=%d", N);
+  if (M == 0) return LRI_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M <= kGemvMaxRows) {
+    LinearParams p{};
+    p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
+    return gemv_launch(dtype, EPI_PLAIN, p, st);
+  }
+  rc = gemm_launch(dtype, x, w, y, M, N, K, st);
+  if (rc != LRI_OK || addend == nullptr) return rc;
+  LRI_REQUIRE((M * N) % 8 == 0 && aligned16(y) && aligned16(addend), LRI_ERR_ALIGN,
+              "linear: addend path needs M*N %% 8 == 0 and 16-byte aligned y, addend");
+  return add_rows_launch(dtype, y, addend, M * N, st);
+}
+
+extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
+  return M <= kGemvMaxRows ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
+}
+
+extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t M, int I, int K,
+                                 void* workspace, size_t workspace_bytes, lri_stream_t stream) {
+  int rc = check_common("gateup_swiglu", dtype, x, w1, M, K);
+  if (rc != LRI_OK) return rc;
+  LRI_REQUIRE(h != nullptr && I > 0, LRI_ERR_ARG, "gateup_swiglu: h is NULL or I=%d", I);
+  if (M == 0) return LRI_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M <= kGemvMaxRows) {
+    LinearParams p{};
+    p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
+    return gemv_launch(dtype, EPI_SWIGLU, p, st);
+  }
+  LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, kGemvMaxRows);
+  LRI_REQUIRE(workspace && workspace_bytes >= lri_gateup_workspace_bytes(M, I) && aligned16(workspace) && aligned16(h),
+              LRI_ERR_WORKSPACE, "gateup_swiglu: workspace of %zu bytes (16-byte aligned) required",
+              lri_gateup_workspace_bytes(M, I));
+  rc = gemm_launch(dtype, x, w1, workspace, M, 2 * I, K, st);
+  if (rc != LRI_OK) return rc;
+  return swiglu_rows_launch(dtype, workspace, h, M, I, st);
+}
+
+extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
+  return M <= kGemvMaxRows ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
+}
+
+extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void* rope_table,
+                                    const void* input_pos, int pos_is_i64, void* q_out, void* k_cache, void* v_cache,
+                                    int B, int S, int K, int n_head, int n_kv, int head_dim, int64_t smax,
+                                    int64_t table_rows, int table_gathered, void* workspace,
+                                    size_t workspace_bytes, lri_stream_t stream) {
+  LRI_REQUIRE(B >= 0 && S >= 0, LRI_ERR_ARG, "qkv_rope_kvcache: B=%d S=%d", B, S);
+  const int64_t M = static_cast<int64_t>(B) * S;
+  int rc = check_common("qkv_rope_kvcache", dtype, x, wqkv, M, K);
+  if (rc != LRI_OK) return rc;
+  LRI_REQUIRE(rope_table && input_pos && q_out && k_cache && v_cache, LRI_ERR_ARG, "qkv_rope_kvcache: NULL pointer");
+  LRI_REQUIRE(n_head > 0 && n_kv > 0 && head_dim > 0 && head_dim % 8 == 0, LRI_ERR_UNSUPPORTED,
+              "qkv_rope_kvcache: n_head=%d n_kv=%d head_dim=%d (head_dim must be a multiple of 8)", n_head, n_kv,
+              head_dim);
+  LRI_REQUIRE(smax > 0 && table_rows > 0, LRI_ERR_ARG, "qkv_rope_kvcache: smax=%lld table_rows=%lld", (long long)smax,
+              (long long)table_rows);
+  LRI_REQUIRE(aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache) && aligned16(rope_table), LRI_ERR_ALIGN,
+              "qkv_rope_kvcache: outputs and table must be 16-byte aligned");
+  if (M == 0) return LRI_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LinearParams p{};
+  p.x = x, p.w = wqkv, p.m = static_cast<int>(M), p.n = (n_head + 2 * n_kv) * head_dim, p.k = K;
+  p.rope_table = rope_table, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64;
+  p.q_out = q_out, p.k_cache = k_cache, p.v_cache = v_cache;
+  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.head_dim = head_dim, p.smax = smax, p.table_rows = table_rows, p.table_gathered = table_gathered;
+  if (M <= kGemvMaxRows) return gemv_launch(dtype, EPI_QKV, p, st);
+  LRI_REQUIRE(workspace && workspace_bytes >= lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
+              LRI_ERR_WORKSPACE, "qkv_rope_kvcache: workspace of %zu bytes (16-byte aligned) required",
+              lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim));
+  rc = gemm_launch(dtype, x, wqkv, workspace, M, p.n, K, st);
+  if (rc != LRI_OK) return rc;
+  return qkv_scatter_launch(dtype, workspace, p, st);
+}

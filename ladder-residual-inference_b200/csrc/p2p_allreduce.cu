@@ -1,0 +1,254 @@
+// F8: one-shot all-reduce over NVLink peer memory for small decode messages.
+//
+// Every rank owns an inbox that all peers have mapped (CUDA IPC):
+//   data  [2][world][max_bytes]      double buffered, one slot per source rank
+//   flags [2][world][kMaxCtas]       epoch-valued arrival flags, one per (source rank, CTA index)
+//   epoch, ticket, status            device-resident bookkeeping
+// A call launches the same grid on every rank.  CTA c of rank r copies its range of the input
+// into slot r of every rank's inbox (plain 16-byte stores over NVLink), publishes the epoch to
+// flag [r][c] of every rank with a system-scope release, waits (bounded by a timer) until all
+// `world` flags [.][c] of its own inbox carry the epoch, and sums the `world` slots of its range
+// in fp32 in rank order, so every rank produces bit-identical results.  The epoch advances from
+// device memory when the last CTA of the grid retires, which keeps replays of a captured CUDA
+// graph correct.  Two buffers are enough: a rank cannot enter call n+2 before every peer has
+// entered call n+1, i.e. finished reading call n.
+#include <cstring>
+
+#include "common.cuh"
+
+struct lri_comm {
+  int rank, world;
+  int64_t max_bytes;   // per slot
+  uint8_t* local;      // this rank's inbox (cudaMalloc)
+  uint8_t* peer[8];    // every rank's inbox as seen from this rank (peer[rank] == local)
+  size_t total_bytes;
+};
+
+namespace lri {
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxCtas = 64;
+constexpr int kArThreads = 256;
+
+struct Control {
+  unsigned int epoch;   // number of completed calls
+  unsigned int ticket;  // CTAs retired in the running call
+  int status;           // LRI_OK or LRI_ERR_TIMEOUT
+  int pad;
+};
+
+__host__ __device__ inline size_t data_bytes(int world, int64_t max_bytes) {
+  return static_cast<size_t>(2) * world * static_cast<size_t>(max_bytes);
+}
+__host__ __device__ inline size_t flags_offset(int world, int64_t max_bytes) { return data_bytes(world, max_bytes); }
+__host__ __device__ inline size_t control_offset(int world, int64_t max_bytes) {
+  return flags_offset(world, max_bytes) + static_cast<size_t>(2) * world * kMaxCtas * sizeof(unsigned int);
+}
+
+struct ArParams {
+  uint8_t* inbox[kMaxWorld];
+  const void* in;
+  void* out;
+  int64_t nvec;  // 16-byte vectors in the message
+  int64_t max_bytes;
+  int rank, world;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
+  uint8_t* mine = p.inbox[p.rank];
+  Control* ctl = reinterpret_cast<Control*>(mine + control_offset(p.world, p.max_bytes));
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&ctl->epoch) + 1u;
+  const int buf = epoch & 1u;
+  const int64_t per_cta = (p.nvec + gridDim.x - 1) / gridDim.x;
+  const int64_t v0 = blockIdx.x * per_cta;
+  const int64_t v1 = (v0 + per_cta < p.nvec) ? v0 + per_cta : p.nvec;
+  const size_t slot_off = (static_cast<size_t>(buf) * p.world + p.rank) * static_cast<size_t>(p.max_bytes);
+
+  // ---- push my range into slot `rank` of every inbox ------------------------------------------------
+  const uint4* src = reinterpret_cast<const uint4*>(p.in);
+  for (int64_t v = v0 + threadIdx.x; v < v1; v += kArThreads) {
+    const uint4 val = src[v];
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r) reinterpret_cast<uint4*>(p.inbox[r] + slot_off)[v] = val;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    unsigned int* flag = reinterpret_cast<unsigned int*>(p.inbox[threadIdx.x] + flags_offset(p.world, p.max_bytes)) +
+                         (static_cast<size_t>(buf) * p.world + p.rank) * kMaxCtas + blockIdx.x;
+    st_release_sys(flag, epoch);
+  }
+
+  // ---- wait for the same CTA of every rank (bounded) --------------------------------------------------
+  __shared__ int gave_up;
+  if (threadIdx.x == 0) gave_up = 0;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const unsigned int* flag =
+        reinterpret_cast<const unsigned int*>(mine + flags_offset(p.world, p.max_bytes)) +
+        (static_cast<size_t>(buf) * p.world + threadIdx.x) * kMaxCtas + blockIdx.x;
+    const unsigned long long t0 = global_ns();
+    while (ld_acquire_sys(flag) != epoch) {
+      if (global_ns() - t0 > p.timeout_ns) {
+        gave_up = 1;
+        atomicExch(&ctl->status, LRI_ERR_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- reduce the slots of my range in rank order ------------------------------------------------------
+  if (!gave_up) {
+    uint4* dst = reinterpret_cast<uint4*>(p.out);
+    const uint8_t* base = mine + static_cast<size_t>(buf) * p.world * static_cast<size_t>(p.max_bytes);
+    for (int64_t v = v0 + threadIdx.x; v < v1; v += kArThreads) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < p.world; ++r) {
+        float f[8];
+        // volatile-strength load: the data was written by another GPU
+        uint4 raw;
+        const uint4* ptr = reinterpret_cast<const uint4*>(base + static_cast<size_t>(r) * p.max_bytes) + v;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "l"(ptr)
+                     : "memory");
+        unpack8<T>(raw, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+      dst[v] = pack8<T>(acc);
+    }
+  }
+
+  // ---- the last CTA to retire advances the epoch ---------------------------------------------------------
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int t = atomicAdd(&ctl->ticket, 1u);
+    if (t == gridDim.x - 1) {
+      ctl->ticket = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(&ctl->epoch) = epoch;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace lri
+
+using namespace lri;
+
+extern "C" int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm** comm_out,
+                               unsigned char ipc_handle_out[64]) {
+  LRI_REQUIRE(comm_out && ipc_handle_out, LRI_ERR_ARG, "comm_create: NULL output");
+  LRI_REQUIRE(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, LRI_ERR_ARG,
+              "comm_create: rank=%d world=%d (world <= %d)", rank, world, kMaxWorld);
+  LRI_REQUIRE(max_elems > 0 && max_elems <= (1ll << 28), LRI_ERR_ARG, "comm_create: max_elems=%lld",
+              (long long)max_elems);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  lri_comm* c = new lri_comm();
+  c->rank = rank, c->world = world;
+  c->max_bytes = ((max_elems * 2 + 255) / 256) * 256;
+  c->total_bytes = control_offset(world, c->max_bytes) + sizeof(Control);
+  for (int i = 0; i < 8; ++i) c->peer[i] = nullptr;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->local), c->total_bytes);
+  if (e != cudaSuccess) {
+    delete c;
+    return fail(LRI_ERR_CUDA, "comm_create: cudaMalloc(%zu) failed: %s", c->total_bytes, cudaGetErrorString(e));
+  }
+  e = cudaMemset(c->local, 0, c->total_bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->local);
+  if (e != cudaSuccess) {
+    cudaFree(c->local);
+    delete c;
+    return fail(LRI_ERR_CUDA, "comm_create: %s", cudaGetErrorString(e));
+  }
+  memcpy(ipc_handle_out, &h, 64);
+  c->peer[rank] = c->local;
+  *comm_out = c;
+  return LRI_OK;
+}
+
+extern "C" int lri_comm_connect(lri_comm* c, const unsigned char* ipc_handles) {
+  LRI_REQUIRE(c && ipc_handles, LRI_ERR_ARG, "comm_connect: NULL argument");
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handles + 64 * r, 64);
+    void* ptr = nullptr;
+    LRI_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peer[r] = static_cast<uint8_t*>(ptr);
+  }
+  return LRI_OK;
+}
+
+extern "C" int lri_allreduce(lri_comm* c, int dtype, const void* in, void* out, int64_t count, int timeout_ms,
+                             lri_stream_t stream) {
+  LRI_REQUIRE(c && in && out, LRI_ERR_ARG, "allreduce: NULL argument");
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "allreduce: dtype %d", dtype);
+  LRI_REQUIRE(count > 0 && count % 8 == 0, LRI_ERR_UNSUPPORTED, "allreduce: count=%lld must be a positive multiple of 8",
+              (long long)count);
+  LRI_REQUIRE(count * 2 <= c->max_bytes, LRI_ERR_ARG, "allreduce: %lld elements exceed the inbox slot (%lld bytes)",
+              (long long)count, (long long)c->max_bytes);
+  LRI_REQUIRE(aligned16(in) && aligned16(out), LRI_ERR_ALIGN, "allreduce: in/out must be 16-byte aligned");
+  for (int r = 0; r < c->world; ++r)
+    LRI_REQUIRE(c->peer[r] != nullptr, LRI_ERR_ARG, "allreduce: peer %d is not connected", r);
+  ArParams p{};
+  for (int r = 0; r < c->world; ++r) p.inbox[r] = c->peer[r];
+  p.in = in, p.out = out, p.nvec = count / 8, p.max_bytes = c->max_bytes, p.rank = c->rank, p.world = c->world;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
+  // one CTA per 8 KiB of message, at most kMaxCtas (every rank derives the same grid from count)
+  int64_t ctas = (p.nvec + 511) / 512;
+  ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == LRI_BF16)
+    allreduce_oneshot_kernel<__nv_bfloat16><<<static_cast<unsigned>(ctas), kArThreads, 0, st>>>(p);
+  else
+    allreduce_oneshot_kernel<__half><<<static_cast<unsigned>(ctas), kArThreads, 0, st>>>(p);
+  LRI_LAUNCH_CHECK("allreduce_oneshot_kernel");
+  return LRI_OK;
+}
+
+extern "C" int lri_comm_status(lri_comm* c, lri_stream_t stream) {
+  LRI_REQUIRE(c, LRI_ERR_ARG, "comm_status: NULL comm");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Control h;
+  uint8_t* ctl = c->local + control_offset(c->world, c->max_bytes);
+  LRI_CUDA(cudaMemcpyAsync(&h, ctl, sizeof(Control), cudaMemcpyDeviceToHost, st));
+  LRI_CUDA(cudaStreamSynchronize(st));
+  if (h.status != LRI_OK) {
+    LRI_CUDA(cudaMemsetAsync(ctl + offsetof(Control, status), 0, sizeof(int), st));
+    LRI_CUDA(cudaStreamSynchronize(st));
+    return fail(LRI_ERR_TIMEOUT, "allreduce: a peer flag did not arrive within the timeout (rank %d)", c->rank);
+  }
+  return LRI_OK;
+}
+
+extern "C" int lri_comm_destroy(lri_comm* c) {
+  if (!c) return LRI_OK;
+  for (int r = 0; r < c->world; ++r)
+    if (r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+  cudaFree(c->local);
+  delete c;
+  return LRI_OK;
+}

@@ -1,0 +1,171 @@
+"""All-reduce back ends for the row-parallel partial sums (one process per GPU).
+
+`all_reduce_async(t)` starts an in-place SUM over the TP group and returns a handle;
+`wait(handle)` makes the CURRENT stream wait for it (a stream dependency, not a host sync).
+Issuing and waiting are separate because the ladder schedule consumes a sublayer's all-reduce
+one sublayer later (the reference: gpt_fast/gpt_ladder_TP.py:323-356 with
+gpt_fast/utils.py:390-397).
+
+  NoComm       world size 1.
+  TorchComm    torch.distributed all_reduce(async_op=True): NCCL runs on c10d's own stream (the
+               dedicated communication stream), gloo in CPU tests.
+  P2PComm      the hand-written one-shot NVLink all-reduce (lri_allreduce) on a dedicated
+               high-priority stream with event fork/join, for messages up to `max_elems`;
+               larger messages go to TorchComm.
+`make_comm()` picks by the LRI_COMM environment variable: "nccl", "p2p" or "auto" (default;
+p2p for small messages when peers are reachable, else nccl).
+"""
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+P2P_MAX_BYTES_DEFAULT = 2 * 1024 * 1024
+
+
+class NoComm:
+    world = 1
+    rank = 0
+    name = "none"
+
+    def all_reduce_async(self, t, rows=None):
+        return None
+
+    def wait(self, handle):
+        return None
+
+    def status(self):
+        return None
+
+
+class TorchComm:
+    name = "torch.distributed"
+
+    def __init__(self):
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+
+    def all_reduce_async(self, t, rows=None):
+        if rows is not None and rows != t.shape[0]:
+            t = t[:rows]
+        return dist.all_reduce(t, async_op=True)
+
+    def wait(self, handle):
+        if handle is not None:
+            handle.wait()
+
+    def status(self):
+        return None
+
+
+class _P2PHandle:
+    __slots__ = ("event",)
+
+    def __init__(self, event):
+        self.event = event
+
+
+class P2PComm:
+    name = "p2p-oneshot"
+
+    def __init__(self, max_bytes=P2P_MAX_BYTES_DEFAULT, timeout_ms=2000):
+        from . import _C
+        self._C = _C
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.timeout_ms = timeout_ms
+        self.max_elems = max_bytes // 2
+        self.fallback = TorchComm()
+        handle = ctypes.c_void_p()
+        ipc = ctypes.create_string_buffer(64)
+        rc = _C.lib.lri_comm_create(self.rank, self.world, self.max_elems, ctypes.byref(handle), ipc)
+        err = _C.lib.lri_last_error().decode() if rc < 0 else ""
+        self.handle = handle if rc == 0 else None
+        # every step that can fail on one rank alone is followed by an exchange of the outcome,
+        # so that all ranks take the same decision and nobody waits in a collective alone
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (rc, bytes(ipc.raw)))
+        if any(g[0] != 0 for g in gathered):
+            self.close()
+            raise RuntimeError(f"P2P all-reduce set-up failed on a rank (local status {rc} {err})")
+        rc = _C.lib.lri_comm_connect(self.handle, b"".join(g[1] for g in gathered))
+        err = _C.lib.lri_last_error().decode() if rc < 0 else ""
+        outcomes = [None] * self.world
+        dist.all_gather_object(outcomes, rc)
+        if any(o != 0 for o in outcomes):
+            self.close()
+            raise RuntimeError(f"P2P all-reduce peer mapping failed on a rank (local status {rc} {err})")
+        # events are created up front: torch records into an existing event during graph capture
+        self.stream = torch.cuda.Stream(priority=-1)
+        self._ready = [torch.cuda.Event() for _ in range(4)]
+        self._done = [torch.cuda.Event() for _ in range(4)]
+        self._n = 0
+
+    def all_reduce_async(self, t, rows=None):
+        if rows is not None and rows != t.shape[0]:
+            t = t[:rows]
+        count = t.numel()
+        if count > self.max_elems or count % 8 != 0:
+            return self.fallback.all_reduce_async(t)
+        i = self._n % 4
+        self._n += 1
+        ready, done = self._ready[i], self._done[i]
+        ready.record()  # on the current (compute) stream: the partial is complete
+        self.stream.wait_event(ready)
+        self._C.check(self._C.lib.lri_allreduce(self.handle, self._C.dtype_code(t.dtype), t.data_ptr(), t.data_ptr(),
+                                                 count, self.timeout_ms, self.stream.cuda_stream))
+        done.record(self.stream)
+        return _P2PHandle(done)
+
+    def wait(self, handle):
+        if handle is None:
+            return
+        if isinstance(handle, _P2PHandle):
+            torch.cuda.current_stream().wait_event(handle.event)
+        else:
+            handle.wait()
+
+    def status(self):
+        """Raises if a bounded peer wait gave up since the last check (synchronises the comm stream)."""
+        self._C.check(self._C.lib.lri_comm_status(self.handle, self.stream.cuda_stream))
+
+    def close(self):
+        if self.handle:
+            self._C.lib.lri_comm_destroy(self.handle)
+            self.handle = None
+
+
+_COMM = None
+
+
+def make_comm():
+    """The process-wide communicator for the TP group (created once)."""
+    global _COMM
+    if _COMM is not None:
+        return _COMM
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world == 1:
+        _COMM = NoComm()
+        return _COMM
+    mode = os.environ.get("LRI_COMM", "auto").lower()
+    if mode not in ("auto", "nccl", "p2p"):
+        raise ValueError(f"LRI_COMM={mode!r}: expected auto, nccl or p2p")
+    use_p2p = mode in ("auto", "p2p") and torch.cuda.is_available() and dist.get_backend() == "nccl" and world <= 8
+    if use_p2p:
+        try:
+            _COMM = P2PComm(max_bytes=int(os.environ.get("LRI_P2P_MAX_BYTES", P2P_MAX_BYTES_DEFAULT)))
+        except RuntimeError:
+            if mode == "p2p":
+                raise
+            _COMM = TorchComm()
+    else:
+        _COMM = TorchComm()
+    return _COMM
+
+
+def reset_comm():
+    global _COMM
+    if isinstance(_COMM, P2PComm):
+        _COMM.close()
+    _COMM = None

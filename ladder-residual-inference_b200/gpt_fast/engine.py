@@ -1,0 +1,177 @@
+"""Whole-model forward of the four tensor-parallel schedules on preallocated buffers.
+
+One `Engine` per model.  `setup()` sizes every intermediate buffer for the largest
+(batch x sequence) the caches allow, so that `forward()` allocates nothing but the returned
+logits, never synchronises with the host, reads positions from the caller's device tensor, and
+can be captured into a CUDA graph together with its communication stream.
+
+All four schedules are sequences of the same step
+
+    residual, normed = F1(residual + pending adds, norm weight)      fused add + RMSNorm
+    partial          = sublayer(normed)                              F2+F3/F4+F5  or  F6+F5
+    handle           = all_reduce_async(partial)
+
+and differ only in WHEN a partial's all-reduce is waited for and added:
+
+  ladder    one sublayer later: attention of layer i is added before attention of layer i+1,
+            MLP of layer i before MLP of layer i+1, so each all-reduce overlaps the next sublayer
+            (reference gpt_fast/gpt_ladder_TP.py:252-284, 312-358)
+  dense     immediately (gpt_fast/gpt_dense_TP.py:274-284)
+  parallel  one fused attention+MLP sublayer and one all-reduce per layer
+            (gpt_fast/gpt_parallel_TP.py:214-226)
+  desync    residual/t is folded into the partial before the all-reduce where a layer's flag is
+            set; no communication where it is not (gpt_fast/gpt_desync_TP.py:350-384)
+"""
+import torch
+
+from .comm import make_comm
+from .ops import decode_splits
+
+_MAX_SPLITS = 64
+
+
+class Engine:
+    def __init__(self, model, family, ops=None, comm=None):
+        self.model = model
+        self.family = family
+        self.cfg = model.config
+        if ops is None:
+            from .ops import CudaOps
+            ops = CudaOps
+        self.ops = ops
+        self.comm = comm if comm is not None else make_comm()
+        self.ready = False
+
+    # ------------------------------------------------------------------------------------------
+    def setup(self, max_batch, max_seq, device, dtype):
+        cfg, t = self.cfg, self.comm.world
+        self.nh, self.nkv, self.hd = cfg.n_head // t, cfg.n_local_heads // t, cfg.head_dim
+        self.inter = cfg.intermediate_size // t
+        self.d = cfg.dim
+        self.max_batch, self.max_seq = max_batch, max_seq
+        rows = max_batch * max_seq
+        self.max_rows = rows
+
+        def buf(cols):
+            return torch.empty(rows, cols, dtype=dtype, device=device)
+
+        self.resid, self.normed = buf(self.d), buf(self.d)
+        self.part_a, self.part_m = buf(self.d), buf(self.d)
+        self.q, self.y = buf(self.nh * self.hd), buf(self.nh * self.hd)
+        self.h = buf(self.inter)
+        nq = self.ops.qkv_workspace_bytes(rows, self.nh, self.nkv, self.hd)
+        ng = self.ops.gateup_workspace_bytes(rows, self.inter)
+        self.ws_qkv = torch.empty(nq, dtype=torch.uint8, device=device) if nq else None
+        self.ws_ug = torch.empty(ng, dtype=torch.uint8, device=device) if ng else None
+        nbytes = self.ops.attn_decode_scratch_bytes(max_batch, self.nh, self.nkv, self.hd, _MAX_SPLITS)
+        self.scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
+        self.ready = True
+
+    # ------------------------------------------------------------------------------------------
+    def _attention(self, att, w_qkv, rows, B, S, pos, out):
+        ops = self.ops
+        kc, vc = att.kv_cache.k_cache, att.kv_cache.v_cache
+        ops.qkv_rope_kvcache(self.normed, w_qkv, self.model.freqs_cis, False, pos, self.q, kc, vc, B, S, self.nh,
+                             self.nkv, self.hd, self.ws_qkv)
+        ops.attention(self.q, kc, vc, pos, self.y, B, S, self.nh, self.nkv, self.hd, self.scratch, self._splits)
+        ops.linear(self.y, att.wo.weight, out, rows)
+
+    def _mlp(self, w1, w2, rows, out, addend=None):
+        self.ops.gateup_swiglu(self.normed, w1, self.h, rows, self.ws_ug)
+        self.ops.linear(self.h, w2, out, rows, addend=addend)
+
+    def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True):
+        """residual += adds (in place), normed = RMSNorm(residual) * weight."""
+        self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps,
+                             self.resid if (write_residual and (add1 is not None or scale != 1.0)) else None,
+                             self.normed, rows, scale)
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, idx, input_pos):
+        assert self.ready, "Caches must be initialized first"
+        B, S = idx.shape
+        assert input_pos.shape[0] == S, "input_pos must hold one position per token column"
+        assert B <= self.max_batch and S <= self.max_seq, "batch or sequence exceeds setup_caches() sizes"
+        if input_pos.dtype not in (torch.int32, torch.int64):
+            input_pos = input_pos.to(torch.int64)
+        rows = B * S
+        self._splits = decode_splits(B, self.nh, self.nkv, self.model.max_seq_length) if S == 1 else 1
+        self.ops.embedding(self.model.tok_embeddings.weight, idx, self.resid)
+        getattr(self, "_run_" + self.family)(rows, B, S, input_pos)
+        logits = torch.empty(B, S, self.cfg.vocab_size, dtype=self.resid.dtype, device=self.resid.device)
+        self.ops.linear(self.normed, self.model.output.weight, logits, rows)
+        return logits
+
+    # Each _run_* leaves RMSNorm(final residual) * norm.weight in self.normed.
+    def _run_ladder(self, rows, B, S, pos):
+        comm, m = self.comm, self.model
+        h_a = h_m = None
+        first = True
+        for layer in m.layers:
+            comm.wait(h_a)
+            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            h_a = comm.all_reduce_async(self.part_a, rows)
+            comm.wait(h_m)
+            self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+            h_m = comm.all_reduce_async(self.part_m, rows)
+            first = False
+        comm.wait(h_a)
+        comm.wait(h_m)
+        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False)
+
+    def _run_dense(self, rows, B, S, pos):
+        comm, m = self.comm, self.model
+        pending = None
+        for layer in m.layers:
+            self._norm(layer.attention_norm.weight, rows, add1=pending)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            comm.wait(comm.all_reduce_async(self.part_a, rows))
+            self._norm(layer.ffn_norm.weight, rows, add1=self.part_a)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+            comm.wait(comm.all_reduce_async(self.part_m, rows))
+            pending = self.part_m
+        self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
+
+    def _run_parallel(self, rows, B, S, pos):
+        comm, m = self.comm, self.model
+        pending = None
+        for layer in m.layers:
+            att = layer.attention
+            self._norm(layer.attention_norm.weight, rows, add1=pending)
+            w = att.wqkv1.weight
+            nqkv = att.qkv_rows
+            self._attention(att, w[:nqkv], rows, B, S, pos, self.part_a)
+            self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a)
+            comm.wait(comm.all_reduce_async(self.part_m, rows))
+            pending = self.part_m
+        self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
+
+    def _run_desync(self, rows, B, S, pos):
+        comm, m = self.comm, self.model
+        t = comm.world
+        pending = None  # a partial that still has to be added to the rank-local residual
+
+        def fold_and_reduce(partial):
+            # residual = all_reduce(partial + residual / t)
+            self.ops.add_rmsnorm(self.resid, partial, None, None, self.cfg.norm_eps, self.resid, None, rows, 1.0 / t)
+            comm.wait(comm.all_reduce_async(self.resid, rows))
+
+        for layer in m.layers:
+            self._norm(layer.attention_norm.weight, rows, add1=pending)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            if layer.do_attention_all_reduce:
+                fold_and_reduce(self.part_a)
+                pending = None
+            else:
+                pending = self.part_a
+            self._norm(layer.ffn_norm.weight, rows, add1=pending)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+            if layer.do_mlp_all_reduce:
+                fold_and_reduce(self.part_m)
+                pending = None
+            else:
+                pending = self.part_m
+        self._norm(m.norm.weight, rows, add1=pending, write_residual=False)

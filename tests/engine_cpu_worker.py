@@ -1,0 +1,75 @@
+"""One gloo rank of the engine-schedule test (started by tests/test_host_cpu.py through
+torch.distributed.run).  Builds the drop-in model on the CPU, swaps the engine's device ops for
+the oracle-based stand-in, replays the reference's golden cases for this world size and checks
+rank 0's logits (all ranks check: ladder, dense and parallel are rank-invariant; desync is
+compared on rank 0 only)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+for p in (HERE, ROOT, os.path.join(ROOT, "ladder-residual-inference_b200")):
+    sys.path.insert(0, p)
+
+dist.init_process_group("gloo")
+
+import golden_util as gu  # noqa: E402
+from cpu_ops import CpuOps  # noqa: E402
+from oracle import ladder_oracle as lo  # noqa: E402
+
+import gpt_fast  # noqa: E402
+from gpt_fast import gpt_dense_TP, gpt_desync_TP, gpt_ladder_TP, gpt_parallel_TP  # noqa: E402
+from gpt_fast.comm import make_comm  # noqa: E402
+
+
+def main():
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mods = {"ladder": (gpt_ladder_TP, gpt_fast.GPTLadder), "dense": (gpt_dense_TP, gpt_fast.GPTDense),
+            "parallel": (gpt_parallel_TP, gpt_fast.GPTParallel), "desync": (gpt_desync_TP, gpt_fast.GPTDesync)}
+    gold = gu.load(world)
+    assert make_comm().world == world
+    for family in gu.FAMILIES:
+        for dtype_name, tp, init in gu.VARIANTS:
+            if tp != world:
+                continue
+            dtype = getattr(torch, dtype_name)
+            cfg = gu.tiny_config(family)
+            full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS[init])
+            mod, cls = mods[family]
+            kw = gu.preset_kwargs(cfg)
+            if family == "desync":
+                kw["reduce_pattern"] = cfg.reduce_pattern
+            mod.transformer_configs["tiny-golden"] = kw
+            model = cls.from_name("tiny-golden").to(dtype).eval()
+            # per-rank parameter layout (the reference's sharding scheme)
+            att = model.layers[0].attention
+            nq = (cfg.n_head + 2 * cfg.n_local_heads) * cfg.head_dim // world
+            if family == "parallel":
+                assert tuple(att.wqkv1.weight.shape) == (nq + 2 * cfg.intermediate_size // world, cfg.dim)
+                assert tuple(att.w2.weight.shape) == (cfg.dim, cfg.intermediate_size // world)
+            else:
+                assert tuple(att.wqkv.weight.shape) == (nq, cfg.dim)
+                assert tuple(model.layers[0].feed_forward.w1.weight.shape) == (2 * cfg.intermediate_size // world, cfg.dim)
+            assert tuple(att.wo.weight.shape) == (cfg.dim, cfg.dim // world)
+            gu.load_shards(model, family, cfg, full, rank, world, dtype)
+            model.setup_caches(max_batch_size=gu.BATCH, max_seq_length=gu.PROMPT + gu.NEW)
+            assert tuple(att.kv_cache.k_cache.shape) == (gu.BATCH, cfg.n_local_heads // world, 24, cfg.head_dim)
+            model._engine.ops = CpuOps
+            key = f"{family}-{dtype_name}-tp{tp}-{init}"
+            steps, prefill_row0 = gu.replay(model.forward, gold, key)
+            ref = torch.from_numpy(gold[key + "/logits"])
+            tol = 2e-5 if dtype == torch.float32 else 2e-2
+            if family != "desync" or rank == 0:
+                err = gu.rel_err(steps, ref)
+                assert err < tol, f"{key} rank {rank}: {err}"
+                assert gu.rel_err(prefill_row0, gold[key + "/prefill_row0"]) < tol
+    dist.barrier()
+    if rank == 0:
+        print("ENGINE-CPU-OK")
+
+
+if __name__ == "__main__":
+    main()

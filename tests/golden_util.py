@@ -46,3 +46,33 @@ def replay(forward, gold, key):
         logits = forward(fed[:, n:n + 1], torch.tensor([PROMPT + n], dtype=torch.int32))
         steps.append(logits[:, -1].float().cpu())
     return torch.stack(steps), prefill_row0
+
+
+def load_shards(model, family, cfg, full, rank, t, dtype):
+    """Copies rank `rank`'s shards of the seeded full weights into a model that has the reference's
+    module tree (the reference itself or the drop-in package)."""
+    from oracle.ladder_oracle import shard_layer
+    with torch.no_grad():
+        model.tok_embeddings.weight.copy_(full["tok_embeddings"].to(dtype))
+        model.output.weight.copy_(full["output"].to(dtype))
+        model.norm.weight.copy_(full["norm"].to(dtype))
+        for i, layer in enumerate(model.layers):
+            sh = shard_layer(cfg, full, i, rank, t, dtype)
+            layer.attention_norm.weight.copy_(sh["attention_norm"])
+            layer.attention.wo.weight.copy_(sh["wo"])
+            if family == "parallel":
+                layer.attention.wqkv1.weight.copy_(sh["wqkv1"])
+                layer.attention.w2.weight.copy_(sh["w2"])
+            else:
+                layer.attention.wqkv.weight.copy_(sh["wqkv"])
+                layer.feed_forward.w1.weight.copy_(sh["w1"])
+                layer.feed_forward.w2.weight.copy_(sh["w2"])
+                layer.ffn_norm.weight.copy_(sh["ffn_norm"])
+
+
+def preset_kwargs(cfg):
+    """ModelArgs keyword arguments of an OracleConfig (for registering a run-time preset)."""
+    kw = dict(block_size=cfg.block_size, vocab_size=cfg.vocab_size, n_layer=cfg.n_layer, n_head=cfg.n_head,
+              n_local_heads=cfg.n_local_heads, dim=cfg.dim, intermediate_size=cfg.intermediate_size,
+              rope_base=cfg.rope_base, norm_eps=cfg.norm_eps, rope_scaling=cfg.rope_scaling)
+    return kw

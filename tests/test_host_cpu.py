@@ -1,0 +1,94 @@
+"""CPU tests: the C-ABI library loads and exports what the header declares, presets resolve to the
+reference's shapes, and the engine's schedules (with a CPU stand-in for the device ops) reproduce
+the oracle at TP = 1 in-process and at TP = 2 over gloo."""
+import json
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import golden_util as gu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from gpt_fast import _C
+    header = open(os.path.join(ROOT, "include", "lri_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(lri_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 20
+    for name in declared:
+        assert hasattr(_C.lib, name), f"{name} is declared in include/lri_b200.h but not exported"
+    assert declared == set(_C.EXPORTED_SYMBOLS), "ctypes signature table and header disagree"
+    assert _C.lib.lri_version() >= 100
+
+
+def test_argument_checks_need_no_gpu():
+    from gpt_fast import _C
+    rc = _C.lib.lri_linear(0, None, None, None, None, 1, 8, 8, None, 0, None)
+    assert rc == -1 and b"NULL" in _C.lib.lri_last_error()
+    rc = _C.lib.lri_add_rmsnorm(7, 16, None, None, 1.0, None, 0.0, 16, None, 1, 8, None)
+    assert rc == -3
+    assert _C.lib.lri_qkv_workspace_bytes(4, 8, 2, 128) == 0
+    assert _C.lib.lri_qkv_workspace_bytes(100, 8, 2, 128) == 100 * 12 * 128 * 2
+    assert _C.lib.lri_gateup_workspace_bytes(100, 512) == 100 * 1024 * 2
+
+
+def test_no_cpu_fallback():
+    """The product must refuse CPU tensors instead of computing somewhere else."""
+    from gpt_fast.utils import RMSNorm
+    with pytest.raises((RuntimeError, TypeError)):
+        RMSNorm(64)(torch.zeros(2, 64, dtype=torch.bfloat16))
+
+
+def test_presets_match_reference_tables():
+    import gpt_fast  # noqa: F401
+    from gpt_fast import gpt_dense_TP, gpt_desync_TP, gpt_ladder_TP, gpt_parallel_TP
+    ref = json.load(open(os.path.join(gu.GOLDEN_DIR, "reference_presets.json")))
+    mods = {"ladder": gpt_ladder_TP, "dense": gpt_dense_TP, "parallel": gpt_parallel_TP, "desync": gpt_desync_TP}
+    for family, table in ref.items():
+        for name, fields in table.items():
+            args = mods[family].ModelArgs.from_name(name)
+            for k, v in fields.items():
+                assert getattr(args, k) == v, f"{family}:{name}.{k}"
+
+
+def test_baseline_shapes_have_presets():
+    from gpt_fast.gpt_ladder_TP import ModelArgs
+    a = ModelArgs.from_name("ladder-llama-1b")
+    assert (a.dim, a.n_layer, a.n_head, a.n_local_heads, a.head_dim, a.intermediate_size, a.rope_base) == (
+        2048, 16, 32, 8, 64, 8192, 500000)
+    a = ModelArgs.from_name("ladder-llama-405b-kv8")
+    assert (a.dim, a.n_layer, a.n_head, a.n_local_heads, a.head_dim) == (16384, 126, 128, 8, 128)
+    with pytest.raises(KeyError):
+        ModelArgs.from_name("no-such-preset")
+
+
+def test_rope_table_matches_reference_fixture():
+    from gpt_fast.utils import precompute_freqs_cis
+    gold = gu.load(1)
+    for name, dtype in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        t = precompute_freqs_cis(64, 64, 500000, dtype)
+        assert (t.float() - torch.from_numpy(gold[f"ops/{name}/rope_table"])).abs().max() <= (
+            1e-6 if dtype == torch.float32 else 2 ** -8)
+        scaling = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192)
+        t = precompute_freqs_cis(32, 128, 500000, dtype, scaling)
+        assert (t.float() - torch.from_numpy(gold[f"ops/{name}/rope_table_scaled"])).abs().max() <= (
+            1e-6 if dtype == torch.float32 else 2 ** -8)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_engine_schedules_on_cpu_ranks(world):
+    """Runs tests/engine_cpu_worker.py as `world` gloo ranks; each checks all four schedules
+    against the golden fixtures of the reference for that TP degree."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29730 + world),
+           os.path.join(ROOT, "tests", "engine_cpu_worker.py")]
+    env = dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ENGINE-CPU-OK" in r.stdout

@@ -1,0 +1,222 @@
+"""Per-kernel parity on the GPU: every fused op, called through the C ABI, against the CPU oracle
+on the same seeded inputs.  Tolerances: the kernels keep the oracle's rounding points, so results
+differ only by fp32 summation order, i.e. by at most one unit in the last place of the 16-bit
+storage type on a small fraction of elements."""
+import math
+
+import pytest
+import torch
+
+import golden_util as gu
+from oracle import ladder_oracle as lo
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.bfloat16, torch.float16]
+
+
+def _ops():
+    from gpt_fast.ops import CudaOps
+    return CudaOps
+
+
+def _C():
+    from gpt_fast import _C as c
+    return c
+
+
+def _ulp_close(got, ref, dtype, frac_exact=0.0, ulps=1.0):
+    """Every element within `ulps` units in the last place of `dtype` (relative to the larger
+    magnitude), and the whole tensor within 2e-3 relative error."""
+    got, ref = got.float().cpu(), ref.float().cpu()
+    assert torch.isfinite(got).all()
+    eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    # near-zero outputs (cancellation) are compared absolutely, at fp32-summation-noise level
+    atol = 1e-5 * ref.abs().max().item()
+    allowed = 2 * ulps * eps * 1.01 * torch.maximum(got.abs(), ref.abs()) + atol
+    excess = ((got - ref).abs() - allowed).max().item()
+    assert excess <= 0, f"element error exceeds {ulps} ulp by {excess:.3e}"
+    assert gu.rel_err(got, ref) < 2e-3
+
+
+def _randn(gen, *shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,dim", [(1, 256), (5, 4096), (3, 16384), (2, 264)])
+def test_add_rmsnorm(dtype, rows, dim):
+    g = torch.Generator().manual_seed(rows * 1000 + dim)
+    r, a, b = (_randn(g, rows, dim, scale=1.5, dtype=dtype) for _ in range(3))
+    w = (1 + 0.3 * torch.randn(dim, generator=g)).to(dtype)
+    ops = _ops()
+    rc, ac, bc, wc = r.cuda(), a.cuda(), b.cuda(), w.cuda()
+    # two-way add + norm, in place on the residual
+    res, normed = rc.clone(), torch.empty_like(rc)
+    ops.add_rmsnorm(res, ac, None, wc, 1e-5, res, normed, rows)
+    ref_res = r + a
+    assert torch.equal(res.cpu(), ref_res)
+    _ulp_close(normed, lo.rmsnorm(ref_res, w, 1e-5), dtype, ulps=2)
+    # three-way add, norm only output
+    normed3 = torch.empty_like(rc)
+    ops.add_rmsnorm(rc, ac, bc, wc, 1e-5, None, normed3, rows)
+    _ulp_close(normed3, lo.rmsnorm(r + a + b, w, 1e-5), dtype, ulps=2)
+    # scaled residual, add only (desync): y + x / t
+    out = torch.empty_like(rc)
+    ops.add_rmsnorm(rc, ac, None, None, 0.0, out, None, rows, 0.25)
+    assert torch.equal(out.cpu(), a + r / 4)
+    # norm only
+    n0 = torch.empty_like(rc)
+    ops.add_rmsnorm(rc, None, None, wc, 1e-5, None, n0, rows)
+    _ulp_close(n0, lo.rmsnorm(r, w, 1e-5), dtype, ulps=2)
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64])
+def test_embedding(idx_dtype):
+    g = torch.Generator().manual_seed(3)
+    table = _randn(g, 1000, 256)
+    idx = torch.randint(0, 1000, (3, 7), generator=g).to(idx_dtype)
+    out = torch.empty(21, 256, dtype=torch.bfloat16, device="cuda")
+    _ops().embedding(table.cuda(), idx.cuda(), out)
+    assert torch.equal(out.cpu(), table[idx.long().view(-1)])
+
+
+GEMV_SHAPES = [(64, 256), (130, 512), (4096, 4096), (1002, 14336), (256, 72), (6, 8)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("n,k", GEMV_SHAPES)
+def test_linear_gemv(dtype, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    x, w = _randn(g, m, k, dtype=dtype), _randn(g, n, k, scale=1 / math.sqrt(k), dtype=dtype)
+    add = _randn(g, m, n, dtype=dtype)
+    y = torch.empty(m, n, dtype=dtype, device="cuda")
+    _ops().linear(x.cuda(), w.cuda(), y, m)
+    _ulp_close(y, lo.linear(x, w), dtype)
+    _ops().linear(x.cuda(), w.cuda(), y, m, addend=add.cuda())
+    _ulp_close(y, lo.linear(x, w) + add, dtype, ulps=2)
+
+
+GEMM_M = [9, 16, 24, 33, 64, 65, 128, 200, 300]
+GEMM_NK = [(64, 64), (136, 72), (512, 256), (1000, 4096), (384, 1024)]
+
+
+@pytest.mark.parametrize("backend", ["tcgen05", "simt"])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", GEMM_M)
+@pytest.mark.parametrize("n,k", GEMM_NK)
+def test_linear_gemm(backend, dtype, m, n, k):
+    c = _C()
+    c.check(c.lib.lri_set_gemm_backend(c.GEMM_TCGEN05 if backend == "tcgen05" else c.GEMM_SIMT))
+    try:
+        g = torch.Generator().manual_seed(m * 7 + n + k)
+        x, w = _randn(g, m, k, dtype=dtype), _randn(g, n, k, scale=1 / math.sqrt(k), dtype=dtype)
+        y = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+        _ops().linear(x.cuda(), w.cuda(), y, m)
+        torch.cuda.synchronize()
+        c.check(c.lib.lri_gemm_status())
+        _ulp_close(y, lo.linear(x, w), dtype)
+    finally:
+        c.lib.lri_set_gemm_backend(c.GEMM_AUTO)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 3, 8, 24, 200])
+@pytest.mark.parametrize("inter,k", [(512, 256), (1000, 1024), (14336 // 8, 4096)])
+def test_gateup_swiglu(dtype, m, inter, k):
+    g = torch.Generator().manual_seed(m + inter + k)
+    x, w1 = _randn(g, m, k, dtype=dtype), _randn(g, 2 * inter, k, scale=2 / math.sqrt(k), dtype=dtype)
+    ops = _ops()
+    h = torch.empty(m, inter, dtype=dtype, device="cuda")
+    nbytes = ops.gateup_workspace_bytes(m, inter)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda") if nbytes else None
+    ops.gateup_swiglu(x.cuda(), w1.cuda(), h, m, ws)
+    _ulp_close(h, lo.swiglu(lo.linear(x, w1)), dtype, ulps=2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,S", [(1, 1), (3, 1), (2, 3), (2, 12), (1, 200)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128)])
+@pytest.mark.parametrize("gathered", [False, True])
+def test_qkv_rope_kvcache(dtype, B, S, nh, nkv, hd, gathered):
+    dim, smax, bmax = 256, 256, 4
+    cfg = lo.OracleConfig(block_size=512, n_head=nh, n_local_heads=nkv, dim=nh * hd, rope_base=500000)
+    g = torch.Generator().manual_seed(B * 100 + S + nh)
+    x = _randn(g, B, S, dim, dtype=dtype)
+    wqkv = _randn(g, (nh + 2 * nkv) * hd, dim, scale=1 / math.sqrt(dim), dtype=dtype)
+    table = lo.rope_table(cfg, dtype)
+    pos = torch.arange(S) + 17 if S > 1 else torch.tensor([41], dtype=torch.int32)
+    kc = _randn(g, bmax, nkv, smax, hd, dtype=dtype)
+    vc = _randn(g, bmax, nkv, smax, hd, dtype=dtype)
+    kref, vref = kc.clone(), vc.clone()
+    qref = lo.qkv_rope_cache(cfg, 1, lo.linear(x, wqkv), table, pos, kref, vref)  # [B, nh, S, hd]
+    ops = _ops()
+    kd, vd = kc.cuda(), vc.cuda()
+    q = torch.empty(B * S, nh * hd, dtype=dtype, device="cuda")
+    nbytes = ops.qkv_workspace_bytes(B * S, nh, nkv, hd)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda") if nbytes else None
+    tab = table[pos.long()].contiguous() if gathered else table
+    ops.qkv_rope_kvcache(x.view(B * S, dim).cuda(), wqkv.cuda(), tab.cuda(), gathered, pos.cuda(), q, kd, vd, B, S, nh,
+                         nkv, hd, ws)
+    _ulp_close(q.view(B, S, nh, hd).transpose(1, 2), qref, dtype, ulps=2)
+    _ulp_close(kd, kref, dtype, ulps=2)
+    _ulp_close(vd, vref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B", [1, 3])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 1, 128), (4, 4, 128), (6, 2, 64), (32, 8, 128)])
+@pytest.mark.parametrize("pos,splits", [(0, 1), (5, 4), (63, 3), (200, 7), (255, 64), (130, 1)])
+def test_attn_decode(dtype, B, nh, nkv, hd, pos, splits):
+    smax, bmax = 256, 3
+    g = torch.Generator().manual_seed(nh * 10 + pos)
+    q = _randn(g, B, nh, 1, hd, dtype=dtype)
+    kc, vc = _randn(g, bmax, nkv, smax, hd, dtype=dtype), _randn(g, bmax, nkv, smax, hd, dtype=dtype)
+    ipos = torch.tensor([pos], dtype=torch.int32)
+    ref = lo.attention_core(q, kc, vc, ipos).transpose(1, 2).reshape(B, nh * hd)
+    ops = _ops()
+    scratch = torch.zeros(ops.attn_decode_scratch_bytes(B, nh, nkv, hd, splits), dtype=torch.uint8, device="cuda")
+    out = torch.empty(B, nh * hd, dtype=dtype, device="cuda")
+    for _ in range(2):  # the second call checks that the arrival counters were left at zero
+        out.fill_(float("nan"))
+        ops.attention(q.view(B, nh * hd).cuda(), kc.cuda(), vc.cuda(), ipos.cuda(), out, B, 1, nh, nkv, hd, scratch,
+                      splits)
+        got = out.float().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - ref.float()).abs().max().item() < 2e-2 * ref.float().abs().max().item() + 1e-3
+        assert gu.rel_err(got, ref) < 6e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,S,pos0", [(1, 12, 0), (2, 64, 0), (1, 65, 0), (2, 130, 7), (1, 300, 0), (1, 2, 100)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128)])
+def test_attn_prefill(dtype, B, S, pos0, nh, nkv, hd):
+    smax, bmax = 320, 2
+    g = torch.Generator().manual_seed(S * 10 + nh)
+    q = _randn(g, B, nh, S, hd, dtype=dtype)
+    kc, vc = _randn(g, bmax, nkv, smax, hd, dtype=dtype), _randn(g, bmax, nkv, smax, hd, dtype=dtype)
+    ipos = torch.arange(S) + pos0
+    ref = lo.attention_core(q, kc, vc, ipos).transpose(1, 2).reshape(B, S, nh * hd)
+    out = torch.full((B, S, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    q_rows = q.transpose(1, 2).contiguous().view(B * S, nh * hd)  # [B, S, nh, hd]
+    _ops().attention(q_rows.cuda(), kc.cuda(), vc.cuda(), ipos.cuda(), out, B, S, nh, nkv, hd, None, 1)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    # probabilities are rounded to the storage type before the PV product (flash-attention practice)
+    assert gu.rel_err(got, ref) < (1.5e-2 if dtype == torch.bfloat16 else 3e-3)
+
+
+def test_argument_errors_are_reported():
+    c = _C()
+    x = torch.zeros(8, 8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        c.check(c.lib.lri_add_rmsnorm(0, x.data_ptr(), None, None, 1.0, x.data_ptr(), 1e-5, None, x.data_ptr(), 1, 12,
+                                      None))
+    with pytest.raises(RuntimeError, match="NULL"):
+        c.check(c.lib.lri_linear(0, None, x.data_ptr(), None, x.data_ptr(), 1, 8, 8, None, 0, None))
+    with pytest.raises(RuntimeError, match="head_dim"):
+        c.check(c.lib.lri_attn_prefill(0, x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 0, x.data_ptr(), 1,
+                                       1, 4, 2, 48, 16, None))
+    with pytest.raises(TypeError):
+        c.dtype_code(torch.float32)
