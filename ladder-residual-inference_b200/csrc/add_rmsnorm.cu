@@ -21,6 +21,8 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
   const uint4* b4 = add2 ? reinterpret_cast<const uint4*>(add2 + row * dim) : nullptr;
   uint4* ro4 = residual_out ? reinterpret_cast<uint4*>(residual_out + row * dim) : nullptr;
 
+  pdl_launch_dependents();
+  pdl_wait();  // the residual and the addends come from the preceding kernels
   float vals[kMaxVecPerThread][8];
   float ss = 0.f;
 #pragma unroll
@@ -100,9 +102,10 @@ template <typename T>
 int launch_add_rmsnorm(const void* residual, const void* add1, const void* add2, float scale,
                        const void* weight, float eps, void* residual_out, void* normed_out, int64_t rows,
                        int dim, cudaStream_t st) {
-  add_rmsnorm_kernel<T><<<static_cast<unsigned>(rows), kNormThreads, 0, st>>>(
-      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
-      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out), dim);
+  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
+                      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
+                      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
+                      dim));
   LRI_LAUNCH_CHECK("add_rmsnorm_kernel");
   return LRI_OK;
 }

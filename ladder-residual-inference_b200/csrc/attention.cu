@@ -16,6 +16,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kDecWarps = 4;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecUnroll = 4;  // positions per row group and loop iteration
+constexpr int kMaxSplits = 64;
 
 struct DecodeParams {
   const void* q;        // [B, n_head, HD]
@@ -51,6 +52,8 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
   const int head0 = kvh * g + (blockIdx.y % tiles_per_kv) * GT;
   const int b = blockIdx.z;
 
+  pdl_launch_dependents();
+  pdl_wait();  // q and the newest cache row were written by the preceding kernel
   int64_t ctx = load_pos(p.input_pos, p.pos_is_i64, 0) + 1;
   ctx = ctx < 0 ? 0 : (ctx > p.smax ? p.smax : ctx);
   const int64_t chunk = (ctx + p.num_splits - 1) / p.num_splits;
@@ -182,21 +185,58 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodePa
   __syncthreads();
   if (ticket_s != static_cast<unsigned int>(p.num_splits - 1)) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < GT * HD; idx += kDecThreads) {
-    const int h = idx / HD, e = idx % HD;
-    const int64_t slot0 = (static_cast<int64_t>(b) * p.n_head + head0 + h) * p.num_splits;
+  // Weights of the splits: one warp per head, lanes over splits, so the (m, l) pairs arrive in one
+  // round trip to L2 instead of one per split.  sm_o is free again and holds the weights.
+  float* wgt = &sm_o[0][0][0];        // [GT][kMaxSplits]
+  float* inv = wgt + GT * kMaxSplits;  // [GT]
+  const int ns = p.num_splits;
+  if (warp < GT) {
+    const int h = warp;
+    const float2* ml = reinterpret_cast<const float2*>(p.part_ml) +
+                       (static_cast<int64_t>(b) * p.n_head + head0 + h) * ns;
+    float2 v[kMaxSplits / 32];
     float mm = -INFINITY;
-    for (int sp = 0; sp < p.num_splits; ++sp) mm = fmaxf(mm, __ldcg(p.part_ml + (slot0 + sp) * 2));
-    float ll = 0.f, oo = 0.f;
-    if (mm > -INFINITY) {
-      for (int sp = 0; sp < p.num_splits; ++sp) {
-        const float w = exp2f(__ldcg(p.part_ml + (slot0 + sp) * 2) - mm);
-        ll += __ldcg(p.part_ml + (slot0 + sp) * 2 + 1) * w;
-        oo += __ldcg(p.part_o + (slot0 + sp) * HD + e) * w;
-      }
+#pragma unroll
+    for (int i = 0; i < kMaxSplits / 32; ++i) {
+      const int sp = lane + 32 * i;
+      v[i] = sp < ns ? __ldcg(ml + sp) : make_float2(-INFINITY, 0.f);
+      mm = fmaxf(mm, v[i].x);
     }
-    const float r = ll > 0.f ? oo / ll : 0.f;
-    static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.n_head + head0 + h) * HD + e] = Num<T>::from_f(r);
+    mm = warp_max(mm);
+    float ll = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxSplits / 32; ++i) {
+      const int sp = lane + 32 * i;
+      const float w = mm == -INFINITY ? 0.f : exp2f(v[i].x - mm);
+      ll += v[i].y * w;
+      if (sp < ns) wgt[h * kMaxSplits + sp] = w;
+    }
+    ll = warp_sum(ll);
+    if (lane == 0) inv[h] = ll > 0.f ? 1.f / ll : 0.f;
+  }
+  __syncthreads();
+  // Outputs: a thread owns 4 consecutive elements of one head and walks the splits with
+  // independent 16-byte loads (unrolled, so several are in flight).
+  for (int idx = threadIdx.x; idx < GT * (HD / 4); idx += kDecThreads) {
+    const int h = idx / (HD / 4), e4 = idx % (HD / 4);
+    const float4* po = reinterpret_cast<const float4*>(p.part_o) +
+                       ((static_cast<int64_t>(b) * p.n_head + head0 + h) * ns) * (HD / 4) + e4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < ns; ++sp) {
+      const float4 o = __ldcg(po + static_cast<int64_t>(sp) * (HD / 4));
+      const float w = wgt[h * kMaxSplits + sp];
+      acc.x = fmaf(o.x, w, acc.x);
+      acc.y = fmaf(o.y, w, acc.y);
+      acc.z = fmaf(o.z, w, acc.z);
+      acc.w = fmaf(o.w, w, acc.w);
+    }
+    const float s = inv[h];
+    T* dst = static_cast<T*>(p.out) + (static_cast<int64_t>(b) * p.n_head + head0 + h) * HD + e4 * 4;
+    uint2 packed;
+    packed.x = pack2<T>(acc.x * s, acc.y * s);
+    packed.y = pack2<T>(acc.z * s, acc.w * s);
+    *reinterpret_cast<uint2*>(dst) = packed;
   }
   if (threadIdx.x == 0) *counter = 0u;  // ready for the next call
 }
@@ -438,11 +478,11 @@ int launch_decode(const DecodeParams& p, int B, cudaStream_t st) {
   const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
   dim3 grid(p.num_splits, p.n_kv * (g / gt), B);
   if (gt == 4)
-    attn_decode_kernel<T, HD, 4><<<grid, kDecThreads, 0, st>>>(p);
+    LRI_CUDA(launch_pdl(attn_decode_kernel<T, HD, 4>, grid, dim3(kDecThreads), 0, st, p));
   else if (gt == 2)
-    attn_decode_kernel<T, HD, 2><<<grid, kDecThreads, 0, st>>>(p);
+    LRI_CUDA(launch_pdl(attn_decode_kernel<T, HD, 2>, grid, dim3(kDecThreads), 0, st, p));
   else
-    attn_decode_kernel<T, HD, 1><<<grid, kDecThreads, 0, st>>>(p);
+    LRI_CUDA(launch_pdl(attn_decode_kernel<T, HD, 1>, grid, dim3(kDecThreads), 0, st, p));
   LRI_LAUNCH_CHECK("attn_decode_kernel");
   return LRI_OK;
 }
@@ -498,7 +538,8 @@ extern "C" int lri_attn_decode(int dtype, const void* q, const void* k_cache, co
   int rc = check_attn("attn_decode", dtype, B, n_head, n_kv, head_dim, smax);
   if (rc != LRI_OK) return rc;
   LRI_REQUIRE(q && k_cache && v_cache && input_pos && out, LRI_ERR_ARG, "attn_decode: NULL pointer");
-  LRI_REQUIRE(num_splits >= 1 && num_splits <= 1024, LRI_ERR_ARG, "attn_decode: num_splits=%d", num_splits);
+  LRI_REQUIRE(num_splits >= 1 && num_splits <= kMaxSplits, LRI_ERR_ARG, "attn_decode: num_splits=%d outside 1..%d",
+              num_splits, kMaxSplits);
   LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
               "attn_decode: pointers must be 16-byte aligned");
   LRI_REQUIRE(scratch && aligned16(scratch) &&

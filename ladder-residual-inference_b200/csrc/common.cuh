@@ -42,6 +42,30 @@ void count_launch(int n = 1);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Programmatic dependent launch.  Kernels of the decode step are launched with the
+// programmatic-stream-serialization attribute: a kernel may start while its predecessor in the
+// stream is still draining, runs the part of its prologue that does not depend on the
+// predecessor (address set-up, streaming the first weight vectors) and then blocks in
+// pdl_wait() until the predecessor has completed and its writes are visible.  Every kernel
+// launched this way calls pdl_wait() before it reads or writes anything another kernel touches.
+// LRI_PDL=0 in the environment turns the attribute off (the device-side calls become no-ops).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- dtype traits ------------------------------------------------------------------------
 template <typename T>
 struct Num;
@@ -99,6 +123,9 @@ template <typename T>
 __device__ __forceinline__ float rnd(float f) {
   return Num<T>::to_f(Num<T>::from_f(f));
 }
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // 16-byte streaming load that does not allocate in L1 (weights are read exactly once)
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {

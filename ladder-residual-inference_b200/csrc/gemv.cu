@@ -51,15 +51,28 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
     for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
 
   const int nchunks = (K + 255) >> 8;
-  for (int c0 = warp; c0 < nchunks; c0 += W * U) {
-    uint4 wv[U][R];
-    uint4 xv[U][M];
+  uint4 wv[U][R];
+  auto load_w = [&](int c0) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = ((c0 + u * W) << 8) + lane * 8;
       const bool ok = k < K;
 #pragma unroll
       for (int r = 0; r < R; ++r) wv[u][r] = ok ? ld_stream16(wrow[r] + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  // The weights do not depend on the preceding kernel: start streaming them, let the next kernel
+  // begin its own prologue, and only then wait for the activations to be complete.
+  int c0 = warp;
+  load_w(c0);
+  pdl_launch_dependents();
+  pdl_wait();
+  while (true) {
+    uint4 xv[U][M];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = ((c0 + u * W) << 8) + lane * 8;
+      const bool ok = k < K;
 #pragma unroll
       for (int m = 0; m < M; ++m)
         xv[u][m] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow[m] + k)) : make_uint4(0, 0, 0, 0);
@@ -79,6 +92,9 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
           for (int e = 0; e < 8; ++e) acc[m][r] = fmaf(wf[e], xf[m][e], acc[m][r]);
       }
     }
+    c0 += W * U;
+    if (c0 >= nchunks) break;
+    load_w(c0);
   }
 
   __shared__ float red[kGemvMaxWarps][M * R];
@@ -127,7 +143,7 @@ int launch_gemv(const LinearParams& p, cudaStream_t st) {
   W = W < 1 ? 1 : (W > kGemvMaxWarps ? kGemvMaxWarps : W);
   const int64_t per_cta = EPI == EPI_SWIGLU ? R / 2 : R;
   const int64_t grid = (p.n + per_cta - 1) / per_cta;
-  gemv_kernel<T, M, R, U, EPI><<<static_cast<unsigned>(grid), W * 32, 0, st>>>(p);
+  LRI_CUDA(launch_pdl(gemv_kernel<T, M, R, U, EPI>, dim3(static_cast<unsigned>(grid)), dim3(W * 32), 0, st, p));
   LRI_LAUNCH_CHECK("gemv_kernel");
   return LRI_OK;
 }

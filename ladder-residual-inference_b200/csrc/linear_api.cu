@@ -38,6 +38,13 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("LRI_PDL");
+    return !(e && strcmp(e, "0") == 0);
+  }();
+  return on;
+}
 int current_gemm_backend() { return g_backend.load(); }
 
 namespace {
