@@ -68,9 +68,9 @@ def measured_hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def shape_of(preset):
-    from gpt_fast.presets import ARCH
-    a = dict(ARCH[preset])
+def shape_of(preset, family="ladder"):
+    from gpt_fast.presets import family_presets
+    a = dict(family_presets(family)[preset])
     a.setdefault("n_local_heads", a["n_head"])
     a.setdefault("vocab_size", 32000)
     if a.get("intermediate_size") is None:
@@ -206,7 +206,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    a = shape_of(args.preset)
+    a = shape_of(args.preset, args.family)
     ctx = args.prompt
     steps, warmup = max(1, min(args.steps, 8)), max(1, min(args.warmup, 2))
     t0 = time.time()
@@ -252,7 +252,7 @@ def run_ours(args):
     assert world == args.gpus, f"--gpus {args.gpus} but the process group has {world} ranks"
     dev = torch.device("cuda", torch.cuda.current_device())
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
-    a = shape_of(args.preset)
+    a = shape_of(args.preset, args.family)
     cls = {"ladder": gpt_fast.GPTLadder, "dense": gpt_fast.GPTDense, "parallel": gpt_fast.GPTParallel,
            "desync": gpt_fast.GPTDesync}[args.family]
     with torch.device("meta"):

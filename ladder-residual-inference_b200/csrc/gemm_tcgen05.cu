@@ -3,7 +3,7 @@
 // One CTA per 128 x BN output tile.  Warp 0 is the TMA producer, warp 1 allocates TMEM and
 // issues tcgen05.mma (one elected thread), warps 2-5 are the epilogue (each reads its own
 // 32-lane quarter of TMEM with tcgen05.ld and stores C).  Operand tiles are 64 K-elements
-// wide (128 bytes per row) and land in shared memory through plain, non-multicast TMA in the
+// wide (128 bytes per row) and land in shared memory through plain single-CTA TMA loads in the
 // 128-byte swizzle, which is also the layout the shared-memory matrix descriptors name.  A
 // ring of mbarrier pairs (full / empty) pipelines the K loop; tcgen05.commit releases a stage.
 //

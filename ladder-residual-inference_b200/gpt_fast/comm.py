@@ -35,6 +35,9 @@ class NoComm:
     def wait(self, handle):
         return None
 
+    def all_reduce(self, t, rows=None):
+        return None
+
     def status(self):
         return None
 
@@ -54,6 +57,12 @@ class TorchComm:
     def wait(self, handle):
         if handle is not None:
             handle.wait()
+
+    def all_reduce(self, t, rows=None):
+        """In-stream all-reduce: later work on the current stream sees the sum."""
+        if rows is not None and rows != t.shape[0]:
+            t = t[:rows]
+        dist.all_reduce(t)
 
     def status(self):
         return None
@@ -125,6 +134,18 @@ class P2PComm:
             torch.cuda.current_stream().wait_event(handle.event)
         else:
             handle.wait()
+
+    def all_reduce(self, t, rows=None):
+        """In-stream all-reduce for schedules that consume the sum at once (dense, parallel,
+        desync): the kernel runs on the current stream, so there is no event fork/join to pay."""
+        if rows is not None and rows != t.shape[0]:
+            t = t[:rows]
+        count = t.numel()
+        if count > self.max_elems or count % 8 != 0:
+            dist.all_reduce(t)
+            return
+        self._C.check(self._C.lib.lri_allreduce(self.handle, self._C.dtype_code(t.dtype), t.data_ptr(), t.data_ptr(),
+                                                 count, self.timeout_ms, torch.cuda.current_stream().cuda_stream))
 
     def status(self):
         """Raises if a bounded peer wait gave up since the last check (synchronises the comm stream)."""

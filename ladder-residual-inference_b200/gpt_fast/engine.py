@@ -128,10 +128,10 @@ class Engine:
         for layer in m.layers:
             self._norm(layer.attention_norm.weight, rows, add1=pending)
             self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
-            comm.wait(comm.all_reduce_async(self.part_a, rows))
+            comm.all_reduce(self.part_a, rows)
             self._norm(layer.ffn_norm.weight, rows, add1=self.part_a)
             self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
-            comm.wait(comm.all_reduce_async(self.part_m, rows))
+            comm.all_reduce(self.part_m, rows)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
 
@@ -145,7 +145,7 @@ class Engine:
             nqkv = att.qkv_rows
             self._attention(att, w[:nqkv], rows, B, S, pos, self.part_a)
             self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a)
-            comm.wait(comm.all_reduce_async(self.part_m, rows))
+            comm.all_reduce(self.part_m, rows)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
 
@@ -157,7 +157,7 @@ class Engine:
         def fold_and_reduce(partial):
             # residual = all_reduce(partial + residual / t)
             self.ops.add_rmsnorm(self.resid, partial, None, None, self.cfg.norm_eps, self.resid, None, rows, 1.0 / t)
-            comm.wait(comm.all_reduce_async(self.resid, rows))
+            comm.all_reduce(self.resid, rows)
 
         for layer in m.layers:
             self._norm(layer.attention_norm.weight, rows, add1=pending)

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_tp2_worker():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29811", os.path.join(ROOT, "tests", "tp_gpu_worker.py")]
-    # NVLS off: a rank that leaves while its memory is bound to a multicast object can fault its peers
+    # NVLS off: a rank that leaves while its memory is bound to an NVLink switch-reduction object can fault its peers
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     sys.stdout.write(r.stdout[-4000:])

@@ -68,7 +68,10 @@ def check_models(comm_name):
     gold = gu.load(world)
     for family in gu.FAMILIES:
         cfg = gu.tiny_config(family)
-        for key_dtype, init, tol in (("bfloat16", "quiet", 2e-2), ("float32", "loud", 3e-2)):
+        # quiet init: the reference's own bf16 run is the fixture.  loud init (tells the schedules
+        # apart): the fixture is the reference's fp32 run, so the parity bar is the bf16 oracle on
+        # the same weights and the fp32 fixture only bounds the distance from above.
+        for key_dtype, init in (("bfloat16", "quiet"), ("float32", "loud")):
             full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS[init])
             model = build(family, cfg, full, torch.bfloat16, "tiny-golden")
             assert model._engine.comm.name == ("p2p-oneshot" if comm_name == "p2p" else "torch.distributed")
@@ -81,8 +84,16 @@ def check_models(comm_name):
             steps, prefill_row0 = gu.replay(fwd, gold, key)
             ref = torch.from_numpy(gold[key + "/logits"])
             if family != "desync" or rank == 0:
-                err = gu.rel_err(steps, ref)
-                assert err < tol, f"{comm_name} {key} rank {rank}: rel err {err:.3e}"
+                if key_dtype == "bfloat16":
+                    err = gu.rel_err(steps, ref)
+                    assert err < 2e-2, f"{comm_name} {key} rank {rank}: rel err {err:.3e}"
+                else:
+                    oracle = lo.OracleModel(family, cfg, full, world, torch.bfloat16, gu.BATCH, gu.PROMPT + gu.NEW)
+                    osteps, _ = gu.replay(oracle.forward, gold, key)
+                    err = gu.rel_err(steps, osteps)
+                    assert err < 2e-2, f"{comm_name} {key} rank {rank}: rel err vs bf16 oracle {err:.3e}"
+                    far = gu.rel_err(steps, ref)
+                    assert far < 1.5 * gu.rel_err(osteps, ref) + 1e-2, f"{comm_name} {key}: {far:.3e} from the fp32 run"
             model._engine.comm.status()
     log(f"models ok with comm={comm_name}")
 
