@@ -8,6 +8,8 @@
 //   PLAIN   store (optionally + addend)                       wo / w2 / LM head
 //   SWIGLU  rows (j, I + j) -> silu(gate) * up                 w1
 //   QKV     rotate adjacent pairs, scatter q / k-cache / v-cache   wqkv
+#include <cstdlib>
+
 #include "linear.cuh"
 
 namespace lri {
@@ -135,9 +137,8 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
   }
 }
 
-template <typename T, int M, int U, int EPI>
+template <typename T, int M, int R, int U, int EPI>
 int launch_gemv(const LinearParams& p, cudaStream_t st) {
-  constexpr int R = 4;
   const int nchunks = (p.k + 255) >> 8;
   int W = (nchunks + U - 1) / U;
   W = W < 1 ? 1 : (W > kGemvMaxWarps ? kGemvMaxWarps : W);
@@ -148,12 +149,34 @@ int launch_gemv(const LinearParams& p, cudaStream_t st) {
   return LRI_OK;
 }
 
+// Rows per CTA.  A CTA keeps R * U = 16 / M-dependent 16-byte weight loads in flight per thread
+// whatever R is; fewer rows per CTA mean more, shorter CTAs (less wave quantisation on small
+// projections), more rows mean fewer reductions.  LRI_GEMV_R=2|4|8 overrides the choice.
+int rows_per_cta(const LinearParams& p) {
+  static const int forced = [] {
+    const char* e = getenv("LRI_GEMV_R");
+    const int v = e ? atoi(e) : 0;
+    return (v == 2 || v == 4 || v == 8) ? v : 0;
+  }();
+  (void)p;
+  return forced ? forced : 4;
+}
+
 template <typename T, int EPI>
 int dispatch_m(const LinearParams& p, cudaStream_t st) {
-  if (p.m <= 1) return launch_gemv<T, 1, 4, EPI>(p, st);
-  if (p.m <= 2) return launch_gemv<T, 2, 4, EPI>(p, st);
-  if (p.m <= 4) return launch_gemv<T, 4, 2, EPI>(p, st);
-  return launch_gemv<T, 8, 1, EPI>(p, st);
+  const int r = rows_per_cta(p);
+#define LRI_GEMV_CASE(M_, U2, U4, U8)                                   \
+  if (p.m <= M_) {                                                      \
+    if (r == 2) return launch_gemv<T, M_, 2, U2, EPI>(p, st);           \
+    if (r == 8) return launch_gemv<T, M_, 8, U8, EPI>(p, st);           \
+    return launch_gemv<T, M_, 4, U4, EPI>(p, st);                       \
+  }
+  LRI_GEMV_CASE(1, 8, 4, 2)
+  LRI_GEMV_CASE(2, 8, 4, 2)
+  LRI_GEMV_CASE(4, 4, 2, 1)
+  LRI_GEMV_CASE(8, 2, 1, 1)
+#undef LRI_GEMV_CASE
+  return fail(LRI_ERR_ARG, "gemv: m=%d", p.m);
 }
 
 template <typename T>
