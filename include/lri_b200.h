@@ -131,6 +131,25 @@ int lri_attn_decode(int dtype, const void* q, const void* k_cache, const void* v
                     int head_dim, int64_t smax, int num_splits, void* scratch,
                     size_t scratch_bytes, lri_stream_t stream);
 
+/* lri_attn_decode_static: the same kernel and arguments as lri_attn_decode, minus the scratch
+ * pointer.  (No counterpart in the reference: it exists for callers of THIS library that may not
+ * allocate - a plug-in that receives only tensors and a stream from its host framework, or a
+ * server whose device memory is fixed before traffic starts and where a cudaMalloc, which
+ * synchronises the device, must never happen while requests are in flight.)  The split partials
+ * and counters live in an 8 MiB array built into the library
+ * (lri_attn_decode_static_scratch_capacity()), held by every GPU that loads it until the process
+ * ends.  A configuration needing more (lri_attn_decode_scratch_bytes(...) > capacity) is refused
+ * with LRI_ERR_WORKSPACE.  Nothing is allocated or freed, here or in anything it calls.
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array:
+ * two calls that overlap on the GPU (different streams) corrupt each other; calls in one stream
+ * are fine, and each call leaves the counters at zero for the next. */
+size_t lri_attn_decode_static_scratch_capacity(void);
+int lri_attn_decode_static(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                           const void* input_pos, int pos_is_i64, void* out, int B, int n_head,
+                           int n_kv, int head_dim, int64_t smax, int num_splits,
+                           lri_stream_t stream);
+
 /* ---- F4: causal GQA prefill attention --------------------------------------------------------
  * q [B, S, n_head, head_dim]; query s has position input_pos[0] + s (positions must be
  * consecutive, as in the reference's only caller, benchmark.py:138) and attends cache positions

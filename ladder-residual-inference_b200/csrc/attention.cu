@@ -583,3 +583,46 @@ extern "C" int lri_attn_prefill(int dtype, const void* q, const void* k_cache, c
     return head_dim == 128 ? launch_prefill<__nv_bfloat16, 128>(p, B, st) : launch_prefill<__nv_bfloat16, 64>(p, B, st);
   return head_dim == 128 ? launch_prefill<__half, 128>(p, B, st) : launch_prefill<__half, 64>(p, B, st);
 }
+
+// =====================================================================================================
+// Decode attention for callers that cannot hand over scratch memory
+// =====================================================================================================
+// Some callers of this library own no allocator they may use on the hot path: a plug-in that is
+// given only tensors and a stream by its host framework, or a serving process whose device
+// memory was planned up front and in which a cudaMalloc (which synchronises the whole device)
+// is forbidden once traffic flows.  For them the split partials and arrival counters of the
+// decode-attention kernel live in the fixed array below, which every GPU that loads this library
+// keeps until the process exits.
+namespace lri {
+namespace {
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB per GPU
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+}  // namespace
+}  // namespace lri
+
+extern "C" size_t lri_attn_decode_static_scratch_capacity(void) { return lri::kStaticScratchBytes; }
+
+extern "C" int lri_attn_decode_static(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                                      const void* input_pos, int pos_is_i64, void* out, int B, int n_head,
+                                      int n_kv, int head_dim, int64_t smax, int num_splits, lri_stream_t stream) {
+  const size_t need = lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits);
+  LRI_REQUIRE(need <= kStaticScratchBytes, LRI_ERR_WORKSPACE,
+              "attn_decode_static: B=%d n_head=%d head_dim=%d num_splits=%d needs %zu bytes of scratch, the built-in "
+              "array holds %zu; lower num_splits or use lri_attn_decode with caller-owned scratch",
+              B, n_head, head_dim, num_splits, need, kStaticScratchBytes);
+  int dev = -1;
+  LRI_CUDA(cudaGetDevice(&dev));
+  LRI_REQUIRE(dev >= 0 && dev < kMaxDevices, LRI_ERR_UNSUPPORTED, "attn_decode_static: device ordinal %d", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the address the kernel must get comes from
+    // the runtime, for the device that is current now.  Done on the first call per device.
+    void* p = nullptr;
+    LRI_CUDA(cudaGetSymbolAddress(&p, g_static_decode_scratch));
+    LRI_REQUIRE(p != nullptr, LRI_ERR_CUDA, "attn_decode_static: no device address for the scratch array");
+    g_static_scratch_ptr[dev] = p;
+  }
+  return lri_attn_decode(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, n_head, n_kv, head_dim, smax,
+                         num_splits, g_static_scratch_ptr[dev], kStaticScratchBytes, stream);
+}

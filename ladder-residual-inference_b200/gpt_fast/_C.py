@@ -45,6 +45,9 @@ _SIGNATURES = {
     "lri_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "lri_attn_decode": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                 c_int, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "lri_attn_decode_static_scratch_capacity": (c_size_t, []),
+    "lri_attn_decode_static": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                       c_int, c_int, c_int64, c_int, c_void_p]),
     "lri_attn_prefill": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_int, c_int, c_int64, c_void_p]),
     "lri_comm_create": (c_int, [c_int, c_int, c_int64, ctypes.POINTER(c_void_p), ctypes.c_char_p]),
