@@ -21,6 +21,16 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
   const uint4* b4 = add2 ? reinterpret_cast<const uint4*>(add2 + row * dim) : nullptr;
   uint4* ro4 = residual_out ? reinterpret_cast<uint4*>(residual_out + row * dim) : nullptr;
 
+  // the norm weight is a constant of the model: fetch it while the preceding kernel drains
+  uint4 wq[kMaxVecPerThread];
+  if (weight != nullptr) {
+    const uint4* w4 = reinterpret_cast<const uint4*>(weight);
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) wq[i] = __ldg(w4 + v);
+    }
+  }
   pdl_launch_dependents();
   pdl_wait();  // the residual and the addends come from the preceding kernels
   float vals[kMaxVecPerThread][8];
@@ -69,14 +79,13 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
   }
   __syncthreads();
   const float inv = inv_shared;
-  const uint4* w4 = reinterpret_cast<const uint4*>(weight);
   uint4* n4 = reinterpret_cast<uint4*>(normed_out + row * dim);
 #pragma unroll
   for (int i = 0; i < kMaxVecPerThread; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
       float w[8], y[8];
-      unpack8<T>(w4[v], w);
+      unpack8<T>(wq[i], w);
 #pragma unroll
       for (int e = 0; e < 8; ++e) y[e] = rnd<T>(vals[i][e] * inv) * w[e];
       n4[v] = pack8<T>(y);

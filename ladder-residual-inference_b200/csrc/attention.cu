@@ -6,6 +6,11 @@
 #include "common.cuh"
 
 namespace lri {
+// cluster form of the decode kernel (attention_cluster.cu)
+bool attn_decode_cluster_supports(int num_splits);
+int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, const void* v_cache,
+                               const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
+                               int head_dim, int64_t smax, int num_splits, float scale_log2, cudaStream_t st);
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -542,6 +547,14 @@ extern "C" int lri_attn_decode(int dtype, const void* q, const void* k_cache, co
               num_splits, kMaxSplits);
   LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
               "attn_decode: pointers must be 16-byte aligned");
+  if (attn_decode_cluster_supports(num_splits)) {
+    // 1, 2, 4 or 8 splits: the splits are the CTAs of one cluster and merge through distributed
+    // shared memory; the scratch buffer is not touched
+    if (B == 0) return LRI_OK;
+    return attn_decode_cluster_launch(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, n_head, n_kv,
+                                      head_dim, smax, num_splits, kLog2e / sqrtf(static_cast<float>(head_dim)),
+                                      static_cast<cudaStream_t>(stream));
+  }
   LRI_REQUIRE(scratch && aligned16(scratch) &&
                   scratch_bytes >= lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits),
               LRI_ERR_WORKSPACE, "attn_decode: scratch of %zu bytes (16-byte aligned) required",

@@ -323,7 +323,8 @@ int launch_typed(int dtype, const void* a, const void* w, void* c, int64_t m, in
   int sms = 148;
   const int64_t mt = (m + kBM - 1) / kBM;
   const int64_t t256 = mt * ((n + 255) / 256), t128 = mt * ((n + 127) / 128);
-  const int64_t cost256 = ((t256 + sms - 1) / sms) * 256, cost128 = ((t128 + sms - 1) / sms) * 128;
+  // measured: a 128x256 tile takes about 1.1x the time of a 128x128 tile (1141 vs 623 TFLOP/s)
+  const int64_t cost256 = ((t256 + sms - 1) / sms) * 110, cost128 = ((t128 + sms - 1) / sms) * 100;
   if (cost256 <= cost128) return launch_tile<T, 256, false>(dtype, a, w, c, m, n, k, st);
   return launch_tile<T, 128, false>(dtype, a, w, c, m, n, k, st);
 }

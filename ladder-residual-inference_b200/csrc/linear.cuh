@@ -63,8 +63,19 @@ __device__ __forceinline__ void qkv_epilogue_pair(const LinearParams& p, int64_t
   }
 }
 
-// decode path, 1 <= p.m <= 8
+// decode path, 1 <= p.m <= 8 (SIMT FMA)
 int gemv_launch(int dtype, int epi, const LinearParams& p, cudaStream_t st);
+// decode path, 1 <= p.m <= 16 (same streaming, tensor-core FMA)
+constexpr int kGemvMmaMaxRows = 16;
+int gemv_mma_launch(int dtype, int epi, const LinearParams& p, cudaStream_t st);
+// Rows up to which the streaming kernels (no workspace) are used, and which of the two runs:
+// one row -> SIMT kernel, 2..16 rows -> tensor-core kernel (LRI_GEMV_SMALL=simt keeps the SIMT
+// kernel up to 8 rows).
+inline int streaming_launch(int dtype, int epi, const LinearParams& p, cudaStream_t st, bool prefer_simt) {
+  if (p.m == 1 || (prefer_simt && p.m <= kGemvMaxRows)) return gemv_launch(dtype, epi, p, st);
+  return gemv_mma_launch(dtype, epi, p, st);
+}
+bool prefer_simt_gemv();
 
 // C[m, n] = A[m, k] * W[n, k]^T, C in `dtype`, any m.  backend: lri_gemm_backend.
 int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);

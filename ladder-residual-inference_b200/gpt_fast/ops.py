@@ -91,12 +91,20 @@ class CudaOps:
                                              smax, _C.stream_handle()))
 
 
-def decode_splits(B, n_head, n_kv, smax, sm_count=148):
-    """Number of sequence ranges for decode attention: enough CTAs for two per SM, but ranges of
-    at least 64 positions.  Fixed per cache geometry so the launch grid never depends on the
-    current position."""
+def decode_splits(B, n_head, n_kv, smax, sm_count=148, head_dim=128):
+    """Number of sequence ranges for decode attention, fixed per cache geometry so that the launch
+    grid never depends on the current position.  Up to 8 ranges (a power of two) run as one
+    thread-block cluster and merge through shared memory; that form is kept as long as a CTA
+    then streams at most ~1 MB of K/V.  Longer caches take more ranges (up to 64, at least 64
+    positions each) and merge through the scratch buffer."""
     g = n_head // n_kv
     gt = 4 if g % 4 == 0 else (2 if g % 2 == 0 else 1)
     base = max(1, B * n_kv * (g // gt))
-    want = -(-2 * sm_count // base)
+    want = max(1, -(-2 * sm_count // base))
+    bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8
+    if want <= 8 or bytes_per_cta_at_8 <= (1 << 20):
+        n = 1
+        while n * 2 <= min(want, 8) and smax // (n * 2) >= 32:
+            n *= 2
+        return n
     return int(max(1, min(want, 64, max(1, smax // 64))))

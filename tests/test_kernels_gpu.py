@@ -91,7 +91,7 @@ GEMV_SHAPES = [(64, 256), (130, 512), (4096, 4096), (1002, 14336), (256, 72), (6
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 13, 16])
 @pytest.mark.parametrize("n,k", GEMV_SHAPES)
 def test_linear_gemv(dtype, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
@@ -128,7 +128,7 @@ def test_linear_gemm(backend, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m", [1, 3, 8, 24, 200])
+@pytest.mark.parametrize("m", [1, 3, 8, 12, 16, 24, 200])
 @pytest.mark.parametrize("inter,k", [(512, 256), (1000, 1024), (14336 // 8, 4096)])
 def test_gateup_swiglu(dtype, m, inter, k):
     g = torch.Generator().manual_seed(m + inter + k)
@@ -142,7 +142,7 @@ def test_gateup_swiglu(dtype, m, inter, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("B,S", [(1, 1), (3, 1), (2, 3), (2, 12), (1, 200)])
+@pytest.mark.parametrize("B,S", [(1, 1), (3, 1), (2, 3), (2, 8), (2, 12), (1, 200)])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128)])
 @pytest.mark.parametrize("gathered", [False, True])
 def test_qkv_rope_kvcache(dtype, B, S, nh, nkv, hd, gathered):
@@ -173,7 +173,8 @@ def test_qkv_rope_kvcache(dtype, B, S, nh, nkv, hd, gathered):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B", [1, 3])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 1, 128), (4, 4, 128), (6, 2, 64), (32, 8, 128)])
-@pytest.mark.parametrize("pos,splits", [(0, 1), (5, 4), (63, 3), (200, 7), (255, 64), (130, 1)])
+@pytest.mark.parametrize("pos,splits", [(0, 1), (5, 4), (63, 3), (200, 7), (255, 64), (130, 1), (100, 8), (17, 2),
+                                        (3, 8)])
 def test_attn_decode(dtype, B, nh, nkv, hd, pos, splits):
     smax, bmax = 256, 3
     g = torch.Generator().manual_seed(nh * 10 + pos)
