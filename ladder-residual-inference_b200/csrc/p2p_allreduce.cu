@@ -46,6 +46,16 @@ __host__ __device__ inline size_t control_offset(int world, int64_t max_bytes) {
   return flags_offset(world, max_bytes) + static_cast<size_t>(2) * world * kMaxCtas * sizeof(unsigned int);
 }
 
+// Low-latency region: messages up to kLlMaxPayload bytes travel as 16-byte lines
+// {data, epoch, data, epoch}: every 8-byte half carries its own arrival flag, so the receiver
+// polls the data itself and neither a fence nor a separate flag store is on the critical path.
+constexpr int64_t kLlMaxPayload = 128 * 1024;
+constexpr int64_t kLlSlotBytes = 2 * kLlMaxPayload;
+__host__ __device__ inline size_t ll_offset(int world, int64_t max_bytes) {
+  return (control_offset(world, max_bytes) + 64 + 255) / 256 * 256;
+}
+__host__ __device__ inline size_t ll_bytes(int world) { return static_cast<size_t>(2) * world * kLlSlotBytes; }
+
 struct ArParams {
   uint8_t* inbox[kMaxWorld];
   const void* in;
@@ -68,6 +78,86 @@ __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+__device__ __forceinline__ void st_volatile16(void* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// One-shot all-reduce, low-latency protocol.  p.nvec counts 8-byte payload units here.  Thread i
+// of the grid owns unit i: it sends the unit as one 16-byte line into slot `rank` of every
+// peer's low-latency region, then polls the `world` lines of that unit in its own region until
+// both halves carry the current epoch, and sums them in rank order (its own contribution comes
+// from registers).  One NVLink crossing, no fence, no flag store.
+template <typename T>
+__global__ void __launch_bounds__(kArThreads) allreduce_ll_kernel(const ArParams p) {
+  uint8_t* mine = p.inbox[p.rank];
+  Control* ctl = reinterpret_cast<Control*>(mine + control_offset(p.world, p.max_bytes));
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&ctl->epoch) + 1u;
+  const int buf = epoch & 1u;
+  const size_t region = ll_offset(p.world, p.max_bytes);
+  const size_t my_slot = region + (static_cast<size_t>(buf) * p.world + p.rank) * kLlSlotBytes;
+  const uint2* src = reinterpret_cast<const uint2*>(p.in);
+  uint2* dst = reinterpret_cast<uint2*>(p.out);
+  const unsigned long long t0 = global_ns();
+  bool gave_up = false;
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * kArThreads + threadIdx.x; u < p.nvec;
+       u += static_cast<int64_t>(gridDim.x) * kArThreads) {
+    const uint2 own = src[u];
+    const uint4 line = make_uint4(own.x, epoch, own.y, epoch);
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r)
+      if (r != p.rank) st_volatile16(p.inbox[r] + my_slot + u * 16, line);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint8_t* lines = mine + region + static_cast<size_t>(buf) * p.world * kLlSlotBytes + u * 16;
+    // first look at all peers' lines at once (independent loads), then re-poll only the late ones
+    uint4 got[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < p.world && r != p.rank) got[r] = ld_volatile16(lines + static_cast<size_t>(r) * kLlSlotBytes);
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r >= p.world) continue;
+      uint2 payload = own;
+      if (r != p.rank) {
+        unsigned int spins = 0;
+        while (!gave_up && (got[r].y != epoch || got[r].w != epoch)) {
+          if ((++spins & 63u) == 0u && global_ns() - t0 > p.timeout_ns) {
+            gave_up = true;
+            atomicExch(&ctl->status, LRI_ERR_TIMEOUT);
+            break;
+          }
+          got[r] = ld_volatile16(lines + static_cast<size_t>(r) * kLlSlotBytes);
+        }
+        payload = make_uint2(got[r].x, got[r].z);
+      }
+      float lo0, hi0, lo1, hi1;
+      Num<T>::unpack2(payload.x, lo0, hi0);
+      Num<T>::unpack2(payload.y, lo1, hi1);
+      acc[0] += lo0, acc[1] += hi0, acc[2] += lo1, acc[3] += hi1;
+    }
+    dst[u] = make_uint2(pack2<T>(acc[0], acc[1]), pack2<T>(acc[2], acc[3]));
+  }
+  // the last CTA to retire advances the epoch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int t = atomicAdd(&ctl->ticket, 1u);
+    if (t == gridDim.x - 1) {
+      ctl->ticket = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(&ctl->epoch) = epoch;
+    }
+  }
 }
 
 template <typename T>
@@ -167,7 +257,7 @@ extern "C" int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm*
   lri_comm* c = new lri_comm();
   c->rank = rank, c->world = world;
   c->max_bytes = ((max_elems * 2 + 255) / 256) * 256;
-  c->total_bytes = control_offset(world, c->max_bytes) + sizeof(Control);
+  c->total_bytes = ll_offset(world, c->max_bytes) + ll_bytes(world);
   for (int i = 0; i < 8; ++i) c->peer[i] = nullptr;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->local), c->total_bytes);
   if (e != cudaSuccess) {
@@ -217,6 +307,19 @@ extern "C" int lri_allreduce(lri_comm* c, int dtype, const void* in, void* out, 
   for (int r = 0; r < c->world; ++r) p.inbox[r] = c->peer[r];
   p.in = in, p.out = out, p.nvec = count / 8, p.max_bytes = c->max_bytes, p.rank = c->rank, p.world = c->world;
   p.timeout_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
+  cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+  if (count * 2 <= kLlMaxPayload && c->world > 1) {
+    // small message: low-latency lines, one 8-byte payload unit per thread
+    p.nvec = count / 4;
+    int64_t blocks = (p.nvec + kArThreads - 1) / kArThreads;
+    blocks = blocks > kMaxCtas ? kMaxCtas : blocks;
+    if (dtype == LRI_BF16)
+      allreduce_ll_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), kArThreads, 0, st0>>>(p);
+    else
+      allreduce_ll_kernel<__half><<<static_cast<unsigned>(blocks), kArThreads, 0, st0>>>(p);
+    LRI_LAUNCH_CHECK("allreduce_ll_kernel");
+    return LRI_OK;
+  }
   // one CTA per 8 KiB of message, at most kMaxCtas (every rank derives the same grid from count)
   int64_t ctas = (p.nvec + 511) / 512;
   ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
