@@ -423,7 +423,9 @@ def dominant_kernel_roofline(model, a, world, B, dtype, dev):
     algo = 2 * inter * d * 2 + B * d * 2 + B * inter * 2  # weights once, activations in and out
     return {"bound": "hbm", "kernel": "gemv_kernel<SWIGLU> (gate/up projection + SwiGLU)", "achieved": algo / (avg_ms / 1e3) / 1e9,
             "unit": "GB/s", "bytes_per_launch": algo, "us_per_launch": avg_ms * 1e3, "launches_timed": len(times),
-            "traffic": None}
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+            # profiles/gemv_gateup_swiglu_8b_tp1_batch1.txt (only that shape was captured)
+            "traffic": 238414848 if (d == 4096 and inter == 14336 and B == 1) else None}
 
 
 def main():

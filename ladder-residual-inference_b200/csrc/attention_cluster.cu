@@ -36,7 +36,7 @@ struct ClusterDecodeParams {
 };
 
 template <typename T, int HD, int GT>
-__global__ void __launch_bounds__(kClThreads) attn_decode_cluster_kernel(const ClusterDecodeParams p) {
+__global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(const ClusterDecodeParams p) {
   constexpr int LPR = HD / 8;    // lanes per cache row
   constexpr int RPW = 32 / LPR;  // row groups per warp
   constexpr int NRG = RPW * kClWarps;

@@ -165,6 +165,12 @@ int rows_per_cta(const LinearParams& p) {
 template <typename T, int EPI>
 int dispatch_m(const LinearParams& p, cudaStream_t st) {
   const int r = rows_per_cta(p);
+  // LRI_GEMV_U=2: half the loads in flight per thread, fewer registers, more resident CTAs (tuning knob)
+  static const bool half_depth = [] {
+    const char* e = getenv("LRI_GEMV_U");
+    return e && atoi(e) == 2;
+  }();
+  if (half_depth && p.m <= 1 && r == 4) return launch_gemv<T, 1, 4, 2, EPI>(p, st);
 #define LRI_GEMV_CASE(M_, U2, U4, U8)                                   \
   if (p.m <= M_) {                                                      \
     if (r == 2) return launch_gemv<T, M_, 2, U2, EPI>(p, st);           \

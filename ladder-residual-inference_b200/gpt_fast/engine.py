@@ -22,6 +22,8 @@ and differ only in WHEN a partial's all-reduce is waited for and added:
   desync    residual/t is folded into the partial before the all-reduce where a layer's flag is
             set; no communication where it is not (gpt_fast/gpt_desync_TP.py:350-384)
 """
+import os
+
 import torch
 
 from .comm import make_comm
@@ -65,6 +67,13 @@ class Engine:
         self.ws_ug = torch.empty(ng, dtype=torch.uint8, device=device) if ng else None
         nbytes = self.ops.attn_decode_scratch_bytes(max_batch, self.nh, self.nkv, self.hd, _MAX_SPLITS)
         self.scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
+        # ladder decode runs the attention and MLP chains of a layer on two streams (LRI_LADDER_OVERLAP=0: one)
+        self.overlap_sublayers = (self.family == "ladder" and self.resid.is_cuda and
+                                  os.environ.get("LRI_LADDER_OVERLAP", "1") != "0")
+        if self.overlap_sublayers:
+            self.normed_m = buf(self.d)
+            self.side_stream = torch.cuda.Stream()
+            self._events = [torch.cuda.Event() for _ in range(2 * cfg.n_layer + 2)]
         self.ready = True
 
     # ------------------------------------------------------------------------------------------
@@ -76,15 +85,15 @@ class Engine:
         ops.attention(self.q, kc, vc, pos, self.y, B, S, self.nh, self.nkv, self.hd, self.scratch, self._splits)
         ops.linear(self.y, att.wo.weight, out, rows)
 
-    def _mlp(self, w1, w2, rows, out, addend=None):
-        self.ops.gateup_swiglu(self.normed, w1, self.h, rows, self.ws_ug)
+    def _mlp(self, w1, w2, rows, out, addend=None, normed=None):
+        self.ops.gateup_swiglu(self.normed if normed is None else normed, w1, self.h, rows, self.ws_ug)
         self.ops.linear(self.h, w2, out, rows, addend=addend)
 
-    def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True):
+    def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True, normed=None):
         """residual += adds (in place), normed = RMSNorm(residual) * weight."""
         self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps,
                              self.resid if (write_residual and (add1 is not None or scale != 1.0)) else None,
-                             self.normed, rows, scale)
+                             self.normed if normed is None else normed, rows, scale)
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -105,6 +114,8 @@ class Engine:
 
     # Each _run_* leaves RMSNorm(final residual) * norm.weight in self.normed.
     def _run_ladder(self, rows, B, S, pos):
+        if S == 1 and self.overlap_sublayers:
+            return self._run_ladder_two_streams(rows, B, S, pos)
         comm, m = self.comm, self.model
         h_a = h_m = None
         first = True
@@ -118,6 +129,49 @@ class Engine:
             self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
             h_m = comm.all_reduce_async(self.part_m, rows)
             first = False
+        comm.wait(h_a)
+        comm.wait(h_m)
+        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False)
+
+    def _run_ladder_two_streams(self, rows, B, S, pos):
+        """Decode form of the ladder schedule.  In a ladder block the MLP of layer i reads the
+        residual BEFORE the attention output of layer i is added, so the attention chain
+        (add+norm, QKV, attention, wo) and the MLP chain (add+norm, gate/up, w2) of one layer do
+        not depend on each other.  They run on two streams: the latency-bound attention kernels
+        hide behind the weight streaming of the MLP, the same slack the reference uses to hide
+        its all-reduces.  Arithmetic and the order of the residual adds are unchanged:
+            main:  r += P_a(i-1); A_i = attn(norm(r))        side:  r += P_m(i-1); M_i = mlp(norm(r))
+        with the side add of layer i ordered after the main add of layer i and before the main add
+        of layer i+1 by events."""
+        comm, m = self.comm, self.model
+        main = torch.cuda.current_stream()
+        side = self.side_stream
+        ev = self._events
+        ev[0].record(main)
+        side.wait_event(ev[0])  # fork (the embedding gather is complete)
+        h_a = h_m = None
+        n = 1
+        first = True
+        for layer in m.layers:
+            e_attn_add, e_mlp_add = ev[n], ev[n + 1]
+            n += 2
+            comm.wait(h_a)
+            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a)
+            e_attn_add.record(main)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            h_a = comm.all_reduce_async(self.part_a, rows)
+            with torch.cuda.stream(side):
+                side.wait_event(e_attn_add)
+                comm.wait(h_m)
+                self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, normed=self.normed_m)
+                e_mlp_add.record(side)
+                self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m,
+                          normed=self.normed_m)
+                h_m = comm.all_reduce_async(self.part_m, rows)
+            main.wait_event(e_mlp_add)  # the next attention add reads the residual the MLP add wrote
+            first = False
+        ev[n].record(side)
+        main.wait_event(ev[n])  # join: the last w2 (and its all-reduce issue) is ordered before the final add
         comm.wait(h_a)
         comm.wait(h_m)
         self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False)
