@@ -93,24 +93,26 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) gemv_mma_kernel(const Linea
       for (int e = 0; e < 4; ++e) acc[mt][t][e] = 0.f;
 
   const int nchunks = (K + kChunk - 1) / kChunk;
-  // Two register buffers of weight vectors: while the MMAs of one chunk run (and wait for its
-  // activations), the loads of the warp's next chunk are already in flight.
-  struct WBuf {
-    uint4 a[MT][BLK], b[MT][BLK];
-  };
-  auto load_w = [&](WBuf& wbuf, int ch) {
+  // One register buffer of weight vectors per thread.  (A second buffer, prefetching the warp's
+  // next chunk during the MMAs, was measured slower: the registers cost a resident CTA per SM.)
+  uint4 wa[MT][BLK], wb[MT][BLK];
+  auto load_w = [&](int ch) {
 #pragma unroll
     for (int j = 0; j < BLK; ++j) {
       const int k = ch * kChunk + j * 32;
-      const bool ok = k + c * 8 < K;  // also false for a chunk past the end
+      const bool ok = k + c * 8 < K;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        wbuf.a[mt][j] = ok ? ld_stream16(w0[mt] + k) : make_uint4(0, 0, 0, 0);
-        wbuf.b[mt][j] = ok ? ld_stream16(w1[mt] + k) : make_uint4(0, 0, 0, 0);
+        wa[mt][j] = ok ? ld_stream16(w0[mt] + k) : make_uint4(0, 0, 0, 0);
+        wb[mt][j] = ok ? ld_stream16(w1[mt] + k) : make_uint4(0, 0, 0, 0);
       }
     }
   };
-  auto compute = [&](const WBuf& wbuf, int ch) {
+  int ch = warp;
+  load_w(ch);  // weights do not depend on the preceding kernel
+  pdl_launch_dependents();
+  pdl_wait();
+  while (true) {
     uint4 xv[NT][BLK];
 #pragma unroll
     for (int j = 0; j < BLK; ++j) {
@@ -126,27 +128,14 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) gemv_mma_kernel(const Linea
       for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          mma16816<T>(acc[mt][t], wbuf.a[mt][j].x, wbuf.b[mt][j].x, wbuf.a[mt][j].y, wbuf.b[mt][j].y, xv[t][j].x,
-                      xv[t][j].y);
-          mma16816<T>(acc[mt][t], wbuf.a[mt][j].z, wbuf.b[mt][j].z, wbuf.a[mt][j].w, wbuf.b[mt][j].w, xv[t][j].z,
-                      xv[t][j].w);
+          mma16816<T>(acc[mt][t], wa[mt][j].x, wb[mt][j].x, wa[mt][j].y, wb[mt][j].y, xv[t][j].x, xv[t][j].y);
+          mma16816<T>(acc[mt][t], wa[mt][j].z, wb[mt][j].z, wa[mt][j].w, wb[mt][j].w, xv[t][j].z, xv[t][j].w);
         }
       }
     }
-  };
-  WBuf w_even, w_odd;
-  int ch = warp;
-  load_w(w_even, ch);  // weights do not depend on the preceding kernel
-  pdl_launch_dependents();
-  pdl_wait();
-  while (ch < nchunks) {
-    load_w(w_odd, ch + W);
-    compute(w_even, ch);
     ch += W;
     if (ch >= nchunks) break;
-    load_w(w_even, ch + W);
-    compute(w_odd, ch);
-    ch += W;
+    load_w(ch);
   }
 
   // ---- reduce the K slices of the warps; warp mt finishes tile mt -----------------------------------

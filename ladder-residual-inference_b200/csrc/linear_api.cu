@@ -45,6 +45,16 @@ bool pdl_enabled() {
   }();
   return on;
 }
+// Token rows up to which the weight-streaming kernels (no workspace) are used; more rows go to the
+// tcgen05 GEMM.  LRI_STREAM_ROWS=1..16 lowers the limit (tuning knob).
+int streaming_rows() {
+  static const int rows = [] {
+    const char* e = getenv("LRI_STREAM_ROWS");
+    const int v = e ? atoi(e) : kGemvMmaMaxRows;
+    return v < 1 ? 1 : (v > kGemvMmaMaxRows ? kGemvMmaMaxRows : v);
+  }();
+  return rows;
+}
 bool prefer_simt_gemv() {
   static const bool simt = [] {
     const char* e = getenv("LRI_GEMV_SMALL");
@@ -240,7 +250,7 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
   LRI_REQUIRE(y != nullptr && N > 0, LRI_ERR_ARG, "linear: y is NULL or N=%d", N);
   if (M == 0) return LRI_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M <= kGemvMmaMaxRows) {
+  if (M <= streaming_rows()) {
     LinearParams p{};
     p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
     return streaming_launch(dtype, EPI_PLAIN, p, st, prefer_simt_gemv());
@@ -253,7 +263,7 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
 }
 
 extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
-  return M <= kGemvMmaMaxRows ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
+  return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
 }
 
 extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t M, int I, int K,
@@ -263,12 +273,12 @@ extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void*
   LRI_REQUIRE(h != nullptr && I > 0, LRI_ERR_ARG, "gateup_swiglu: h is NULL or I=%d", I);
   if (M == 0) return LRI_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M <= kGemvMmaMaxRows) {
+  if (M <= streaming_rows()) {
     LinearParams p{};
     p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
     return streaming_launch(dtype, EPI_SWIGLU, p, st, prefer_simt_gemv());
   }
-  LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, kGemvMmaMaxRows);
+  LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, streaming_rows());
   LRI_REQUIRE(workspace && workspace_bytes >= lri_gateup_workspace_bytes(M, I) && aligned16(workspace) && aligned16(h),
               LRI_ERR_WORKSPACE, "gateup_swiglu: workspace of %zu bytes (16-byte aligned) required",
               lri_gateup_workspace_bytes(M, I));
@@ -278,7 +288,7 @@ extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void*
 }
 
 extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
-  return M <= kGemvMmaMaxRows ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
+  return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
 }
 
 extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void* rope_table,
@@ -305,7 +315,7 @@ extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, 
   p.rope_table = rope_table, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64;
   p.q_out = q_out, p.k_cache = k_cache, p.v_cache = v_cache;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.head_dim = head_dim, p.smax = smax, p.table_rows = table_rows, p.table_gathered = table_gathered;
-  if (M <= kGemvMmaMaxRows) return streaming_launch(dtype, EPI_QKV, p, st, prefer_simt_gemv());
+  if (M <= streaming_rows()) return streaming_launch(dtype, EPI_QKV, p, st, prefer_simt_gemv());
   LRI_REQUIRE(workspace && workspace_bytes >= lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
               LRI_ERR_WORKSPACE, "qkv_rope_kvcache: workspace of %zu bytes (16-byte aligned) required",
               lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim));

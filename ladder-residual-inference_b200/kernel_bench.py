@@ -85,8 +85,10 @@ def main():
     nqkv = (nh + 2 * nkv) * hd
     add("qkv_rope_kvcache", nqkv * d * 2 + B * d * 2 + B * nqkv * 2,
         lambda: (rnd(B, d, scale=1), rnd(nqkv, d), torch.empty(B, nh * hd, dtype=dt, device=dev),
-                 torch.zeros(B, nkv, smax, hd, dtype=dt, device=dev), torch.zeros(B, nkv, smax, hd, dtype=dt, device=dev)),
-        lambda o: ops.qkv_rope_kvcache(o[0], o[1], table, False, pos, o[2], o[3], o[4], B, 1, nh, nkv, hd, None))
+                 torch.zeros(B, nkv, smax, hd, dtype=dt, device=dev), torch.zeros(B, nkv, smax, hd, dtype=dt, device=dev),
+                 (torch.empty(ops.qkv_workspace_bytes(B, nh, nkv, hd), dtype=torch.uint8, device=dev)
+                  if ops.qkv_workspace_bytes(B, nh, nkv, hd) else None)),
+        lambda o: ops.qkv_rope_kvcache(o[0], o[1], table, False, pos, o[2], o[3], o[4], B, 1, nh, nkv, hd, o[5]))
     # F3: decode attention
     splits = decode_splits(B, nh, nkv, smax)
     kv_bytes = 2 * B * nkv * args.ctx * hd * 2
