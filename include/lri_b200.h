@@ -179,6 +179,25 @@ int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm** comm_out,
 int lri_comm_connect(lri_comm* comm, const unsigned char* ipc_handles /* host, world*64 */);
 int lri_allreduce(lri_comm* comm, int dtype, const void* in, void* out, int64_t count,
                   int timeout_ms, lri_stream_t stream);
+/* Split form of the all-reduce for small messages (up to lri_comm_push_max_elems() elements): the
+ * producer pushes its partial into the peers' inboxes right after the row-parallel projection
+ * (lri_comm_push, channel 1 or 2, each with its own device-resident epoch), and the reduction
+ * happens inside the consumer: lri_add_rmsnorm_gather is lri_add_rmsnorm whose addend k is, when
+ * channel_k > 0, the SUM over ranks of the message last pushed on that channel (add_k then points
+ * to this rank's own partial; rank-order fp32 sum, rounded once, bit-identical on all ranks) and,
+ * when channel_k == 0, a plain addend pointer or NULL.  No reduce kernel and no stream fork: an
+ * all-reduce costs one small push kernel.  A rank must consume message n of a channel before it
+ * pushes message n+1 on it (two buffers per channel), which every schedule here does; all ranks
+ * push the same sequence.  The consumer's wait is bounded by timeout_ms (status word as above).
+ * Replaces: all_reduce_func + the residual add + RMSNorm that follow it,
+ * gpt_fast/gpt_ladder_TP.py:323-356, gpt_fast/gpt_dense_TP.py:281-282. */
+int64_t lri_comm_push_max_elems(void);
+int lri_comm_push(lri_comm* comm, int channel, int dtype, const void* in, int64_t count,
+                  lri_stream_t stream);
+int lri_add_rmsnorm_gather(lri_comm* comm, int dtype, const void* residual, int channel1,
+                           const void* add1, int channel2, const void* add2, float residual_scale,
+                           const void* weight, float eps, void* residual_out, void* normed_out,
+                           int64_t rows, int dim, int timeout_ms, lri_stream_t stream);
 /* Reads (and clears) the device status word: LRI_OK or LRI_ERR_TIMEOUT.  Synchronises `stream`. */
 int lri_comm_status(lri_comm* comm, lri_stream_t stream);
 int lri_comm_destroy(lri_comm* comm);

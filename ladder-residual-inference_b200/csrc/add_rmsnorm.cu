@@ -1,7 +1,7 @@
 // F1: residual add (two- or three-way, optional residual scale) fused with RMSNorm, plus the
 // embedding gather.  One CTA per token row; the row stays in registers between the add, the
 // mean-square reduction and the normalisation, so it is read once and each output written once.
-#include "common.cuh"
+#include "p2p_ll.cuh"
 
 namespace lri {
 namespace {
@@ -9,11 +9,13 @@ namespace {
 constexpr int kNormThreads = 256;
 constexpr int kMaxVecPerThread = 8;  // 256 threads * 8 vectors * 8 elements = dim up to 16384
 
-template <typename T>
+// GATHER: an addend whose source is enabled in `g` is not read from a pointer but summed over the
+// ranks' low-latency lines (the reduction half of an all-reduce, done where the sum is used).
+template <typename T, bool GATHER>
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, const T* __restrict__ add2,
                    float residual_scale, const T* __restrict__ weight, float eps, T* residual_out,
-                   T* __restrict__ normed_out, int dim) {
+                   T* __restrict__ normed_out, int dim, const GatherArgs g) {
   const int64_t row = blockIdx.x;
   const int nvec = dim >> 3;
   const uint4* r4 = reinterpret_cast<const uint4*>(residual + row * dim);
@@ -33,6 +35,13 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
   }
   pdl_launch_dependents();
   pdl_wait();  // the residual and the addends come from the preceding kernels
+  unsigned int epoch1 = 0, epoch2 = 0;
+  unsigned long long t0 = 0;
+  if (GATHER) {
+    if (g.s1.enabled) epoch1 = *reinterpret_cast<const volatile unsigned int*>(g.s1.epoch_ptr);
+    if (g.s2.enabled) epoch2 = *reinterpret_cast<const volatile unsigned int*>(g.s2.epoch_ptr);
+    t0 = ll_global_ns();
+  }
   float vals[kMaxVecPerThread][8];
   float ss = 0.f;
 #pragma unroll
@@ -45,13 +54,23 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = rnd<T>(x[e] * residual_scale);
       }
-      if (a4) {
+      if (GATHER && g.s1.enabled) {
+        float a[8];
+        ll_gather8<T>(g.s1, epoch1, row * dim + static_cast<int64_t>(v) * 8, a, t0);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = rnd<T>(x[e] + a[e]);
+      } else if (a4) {
         float a[8];
         unpack8<T>(a4[v], a);
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = rnd<T>(x[e] + a[e]);
       }
-      if (b4) {
+      if (GATHER && g.s2.enabled) {
+        float b[8];
+        ll_gather8<T>(g.s2, epoch2, row * dim + static_cast<int64_t>(v) * 8, b, t0);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = rnd<T>(x[e] + b[e]);
+      } else if (b4) {
         float b[8];
         unpack8<T>(b4[v], b);
 #pragma unroll
@@ -111,15 +130,39 @@ template <typename T>
 int launch_add_rmsnorm(const void* residual, const void* add1, const void* add2, float scale,
                        const void* weight, float eps, void* residual_out, void* normed_out, int64_t rows,
                        int dim, cudaStream_t st) {
-  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
+  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
                       static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
                       static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
-                      dim));
+                      dim, GatherArgs{}));
   LRI_LAUNCH_CHECK("add_rmsnorm_kernel");
   return LRI_OK;
 }
 
+template <typename T>
+int launch_gather_typed(const void* residual, const void* add1, const void* add2, float scale, const void* weight,
+                        float eps, void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g,
+                        cudaStream_t st) {
+  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
+                      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
+                      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
+                      dim, g));
+  LRI_LAUNCH_CHECK("add_rmsnorm_kernel<gather>");
+  return LRI_OK;
+}
+
 }  // namespace
+
+int launch_add_rmsnorm_gather(int dtype, const void* residual, const void* add1, const void* add2, float scale,
+                              const void* weight, float eps, void* residual_out, void* normed_out, int64_t rows,
+                              int dim, const GatherArgs& g, cudaStream_t st) {
+  if (dim <= 0 || dim % 8 != 0 || dim > kNormThreads * kMaxVecPerThread * 8)
+    return fail(LRI_ERR_UNSUPPORTED, "add_rmsnorm_gather: dim=%d", dim);
+  if (rows <= 0) return LRI_OK;
+  return dtype == LRI_BF16 ? launch_gather_typed<__nv_bfloat16>(residual, add1, add2, scale, weight, eps, residual_out,
+                                                                normed_out, rows, dim, g, st)
+                           : launch_gather_typed<__half>(residual, add1, add2, scale, weight, eps, residual_out,
+                                                         normed_out, rows, dim, g, st);
+}
 }  // namespace lri
 
 extern "C" int lri_add_rmsnorm(int dtype, const void* residual, const void* add1, const void* add2,

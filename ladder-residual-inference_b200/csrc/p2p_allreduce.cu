@@ -12,9 +12,10 @@
 // device memory when the last CTA of the grid retires, which keeps replays of a captured CUDA
 // graph correct.  Two buffers are enough: a rank cannot enter call n+2 before every peer has
 // entered call n+1, i.e. finished reading call n.
+#include <cstddef>
 #include <cstring>
 
-#include "common.cuh"
+#include "p2p_ll.cuh"
 
 struct lri_comm {
   int rank, world;
@@ -36,6 +37,8 @@ struct Control {
   unsigned int ticket;  // CTAs retired in the running call
   int status;           // LRI_OK or LRI_ERR_TIMEOUT
   int pad;
+  unsigned int chan_epoch[4];   // per push channel: number of completed pushes
+  unsigned int chan_ticket[4];  // per push channel: CTAs retired in the running push
 };
 
 __host__ __device__ inline size_t data_bytes(int world, int64_t max_bytes) {
@@ -55,6 +58,12 @@ __host__ __device__ inline size_t ll_offset(int world, int64_t max_bytes) {
   return (control_offset(world, max_bytes) + 64 + 255) / 256 * 256;
 }
 __host__ __device__ inline size_t ll_bytes(int world) { return static_cast<size_t>(2) * world * kLlSlotBytes; }
+// Line regions: region 0 belongs to lri_allreduce, regions 1..kPushChannels to the push channels
+// (producer lri_comm_push, consumer lri_add_rmsnorm_gather), each with its own epoch counter.
+constexpr int kPushChannels = 2;
+__host__ __device__ inline size_t ll_region(int world, int64_t max_bytes, int region) {
+  return ll_offset(world, max_bytes) + static_cast<size_t>(region) * ll_bytes(world);
+}
 
 struct ArParams {
   uint8_t* inbox[kMaxWorld];
@@ -160,6 +169,38 @@ __global__ void __launch_bounds__(kArThreads) allreduce_ll_kernel(const ArParams
   }
 }
 
+// Producer half of the split all-reduce: store this rank's partial as lines into slot `rank` of
+// every peer's region of push channel `ch` (1-based).  The channel's epoch advances when the last
+// CTA retires; the consumer (the gathering add + RMSNorm) reads it from there.
+__global__ void __launch_bounds__(kArThreads) ll_push_kernel(const ArParams p, int ch) {
+  pdl_launch_dependents();
+  pdl_wait();  // the partial comes from the preceding kernel
+  uint8_t* mine = p.inbox[p.rank];
+  Control* ctl = reinterpret_cast<Control*>(mine + control_offset(p.world, p.max_bytes));
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&ctl->chan_epoch[ch]) + 1u;
+  const int buf = epoch & 1u;
+  const size_t my_slot = ll_region(p.world, p.max_bytes, ch) + (static_cast<size_t>(buf) * p.world + p.rank) * kLlSlotBytes;
+  const uint2* src = reinterpret_cast<const uint2*>(p.in);
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * kArThreads + threadIdx.x; u < p.nvec;
+       u += static_cast<int64_t>(gridDim.x) * kArThreads) {
+    const uint2 own = src[u];
+    const uint4 line = make_uint4(own.x, epoch, own.y, epoch);
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r)
+      if (r != p.rank) st_volatile16(p.inbox[r] + my_slot + u * 16, line);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int t = atomicAdd(&ctl->chan_ticket[ch], 1u);
+    if (t == gridDim.x - 1) {
+      ctl->chan_ticket[ch] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(&ctl->chan_epoch[ch]) = epoch;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
   uint8_t* mine = p.inbox[p.rank];
@@ -257,7 +298,7 @@ extern "C" int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm*
   lri_comm* c = new lri_comm();
   c->rank = rank, c->world = world;
   c->max_bytes = ((max_elems * 2 + 255) / 256) * 256;
-  c->total_bytes = ll_offset(world, c->max_bytes) + ll_bytes(world);
+  c->total_bytes = ll_region(world, c->max_bytes, 1 + kPushChannels);
   for (int i = 0; i < 8; ++i) c->peer[i] = nullptr;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->local), c->total_bytes);
   if (e != cudaSuccess) {
@@ -330,6 +371,74 @@ extern "C" int lri_allreduce(lri_comm* c, int dtype, const void* in, void* out, 
     allreduce_oneshot_kernel<__half><<<static_cast<unsigned>(ctas), kArThreads, 0, st>>>(p);
   LRI_LAUNCH_CHECK("allreduce_oneshot_kernel");
   return LRI_OK;
+}
+
+extern "C" int64_t lri_comm_push_max_elems(void) { return kLlMaxPayload / 2; }
+
+extern "C" int lri_comm_push(lri_comm* c, int channel, int dtype, const void* in, int64_t count, lri_stream_t stream) {
+  LRI_REQUIRE(c && in, LRI_ERR_ARG, "comm_push: NULL argument");
+  LRI_REQUIRE(channel >= 1 && channel <= kPushChannels, LRI_ERR_ARG, "comm_push: channel %d outside 1..%d", channel,
+              kPushChannels);
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "comm_push: dtype %d", dtype);
+  LRI_REQUIRE(count > 0 && count % 8 == 0 && count * 2 <= kLlMaxPayload, LRI_ERR_UNSUPPORTED,
+              "comm_push: count=%lld must be a positive multiple of 8 and at most %lld", (long long)count,
+              (long long)(kLlMaxPayload / 2));
+  LRI_REQUIRE(aligned16(in), LRI_ERR_ALIGN, "comm_push: input must be 16-byte aligned");
+  for (int r = 0; r < c->world; ++r)
+    LRI_REQUIRE(c->peer[r] != nullptr, LRI_ERR_ARG, "comm_push: peer %d is not connected", r);
+  ArParams p{};
+  for (int r = 0; r < c->world; ++r) p.inbox[r] = c->peer[r];
+  p.in = in, p.out = nullptr, p.nvec = count / 4, p.max_bytes = c->max_bytes, p.rank = c->rank, p.world = c->world;
+  int64_t blocks = (p.nvec + kArThreads - 1) / kArThreads;
+  blocks = blocks > kMaxCtas ? kMaxCtas : blocks;
+  LRI_CUDA(launch_pdl(ll_push_kernel, dim3(static_cast<unsigned>(blocks)), dim3(kArThreads), 0,
+                      static_cast<cudaStream_t>(stream), p, channel));
+  LRI_LAUNCH_CHECK("ll_push_kernel");
+  return LRI_OK;
+}
+
+static int fill_source(lri_comm* c, int channel, const void* own, int64_t count, int timeout_ms, LlSource* s) {
+  s->enabled = 0;
+  if (channel <= 0) return LRI_OK;
+  LRI_REQUIRE(channel <= kPushChannels, LRI_ERR_ARG, "add_rmsnorm_gather: channel %d outside 1..%d", channel,
+              kPushChannels);
+  LRI_REQUIRE(own != nullptr && aligned16(own), LRI_ERR_ARG,
+              "add_rmsnorm_gather: the rank's own partial is required (16-byte aligned) for a gathered addend");
+  LRI_REQUIRE(count * 2 <= kLlMaxPayload, LRI_ERR_UNSUPPORTED, "add_rmsnorm_gather: %lld elements exceed a push message",
+              (long long)count);
+  uint8_t* ctl = c->local + control_offset(c->world, c->max_bytes);
+  s->region = c->local + ll_region(c->world, c->max_bytes, channel);
+  s->epoch_ptr = reinterpret_cast<const unsigned int*>(ctl + offsetof(Control, chan_epoch)) + channel;
+  s->status_ptr = reinterpret_cast<int*>(ctl + offsetof(Control, status));
+  s->own = own;
+  s->slot_bytes = kLlSlotBytes;
+  s->timeout_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
+  s->world = c->world, s->rank = c->rank;
+  s->enabled = 1;
+  return LRI_OK;
+}
+
+extern "C" int lri_add_rmsnorm_gather(lri_comm* c, int dtype, const void* residual, int channel1, const void* add1,
+                                      int channel2, const void* add2, float residual_scale, const void* weight,
+                                      float eps, void* residual_out, void* normed_out, int64_t rows, int dim,
+                                      int timeout_ms, lri_stream_t stream) {
+  LRI_REQUIRE(c && residual, LRI_ERR_ARG, "add_rmsnorm_gather: NULL argument");
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "add_rmsnorm_gather: dtype %d", dtype);
+  LRI_REQUIRE(rows >= 0 && rows < (1ll << 31) && dim > 0, LRI_ERR_ARG, "add_rmsnorm_gather: rows=%lld dim=%d",
+              (long long)rows, dim);
+  LRI_REQUIRE((normed_out == nullptr) == (weight == nullptr), LRI_ERR_ARG,
+              "add_rmsnorm_gather: weight and normed_out must both be given or both be NULL");
+  LRI_REQUIRE(normed_out != nullptr || residual_out != nullptr, LRI_ERR_ARG, "add_rmsnorm_gather: no output");
+  LRI_REQUIRE(aligned16(residual) && aligned16(add1) && aligned16(add2) && aligned16(weight) &&
+                  aligned16(residual_out) && aligned16(normed_out),
+              LRI_ERR_ALIGN, "add_rmsnorm_gather: pointers must be 16-byte aligned");
+  GatherArgs g{};
+  int rc = fill_source(c, channel1, add1, rows * dim, timeout_ms, &g.s1);
+  if (rc != LRI_OK) return rc;
+  rc = fill_source(c, channel2, add2, rows * dim, timeout_ms, &g.s2);
+  if (rc != LRI_OK) return rc;
+  return launch_add_rmsnorm_gather(dtype, residual, add1, add2, residual_scale, weight, eps, residual_out, normed_out,
+                                   rows, dim, g, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int lri_comm_status(lri_comm* c, lri_stream_t stream) {

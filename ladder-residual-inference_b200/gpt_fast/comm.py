@@ -29,6 +29,9 @@ class NoComm:
     rank = 0
     name = "none"
 
+    def can_split(self, count):
+        return False
+
     def all_reduce_async(self, t, rows=None):
         return None
 
@@ -44,6 +47,9 @@ class NoComm:
 
 class TorchComm:
     name = "torch.distributed"
+
+    def can_split(self, count):
+        return False
 
     def __init__(self):
         self.world = dist.get_world_size()
@@ -110,6 +116,8 @@ class P2PComm:
         self._ready = [torch.cuda.Event() for _ in range(4)]
         self._done = [torch.cuda.Event() for _ in range(4)]
         self._n = 0
+        self._push_max = _C.lib.lri_comm_push_max_elems()
+        self.split_enabled = os.environ.get("LRI_SPLIT_AR", "1") != "0"
 
     def all_reduce_async(self, t, rows=None):
         if rows is not None and rows != t.shape[0]:
@@ -146,6 +154,25 @@ class P2PComm:
             return
         self._C.check(self._C.lib.lri_allreduce(self.handle, self._C.dtype_code(t.dtype), t.data_ptr(), t.data_ptr(),
                                                  count, self.timeout_ms, torch.cuda.current_stream().cuda_stream))
+
+    # ---- split all-reduce: push now, reduce inside the consuming add + RMSNorm ----------------
+    def can_split(self, count):
+        """True when a message of `count` elements can take the push / gather path."""
+        return self.split_enabled and count % 8 == 0 and count <= self._push_max
+
+    def push(self, t, rows, channel):
+        """Store rows [0, rows) of `t` into every peer's inbox on push channel 1 or 2 (current stream)."""
+        count = rows * t.shape[1]
+        self._C.check(self._C.lib.lri_comm_push(self.handle, channel, self._C.dtype_code(t.dtype), t.data_ptr(), count,
+                                                torch.cuda.current_stream().cuda_stream))
+
+    def add_rmsnorm_gather(self, residual, ch1, add1, ch2, add2, weight, eps, residual_out, normed_out, rows, scale=1.0):
+        """lri_add_rmsnorm with addends summed over the ranks' pushed messages (channel > 0)."""
+        C = self._C
+        C.check(C.lib.lri_add_rmsnorm_gather(self.handle, C.dtype_code(residual.dtype), residual.data_ptr(), ch1,
+                                             C.ptr(add1), ch2, C.ptr(add2), float(scale), C.ptr(weight), float(eps),
+                                             C.ptr(residual_out), C.ptr(normed_out), rows, residual.shape[-1],
+                                             self.timeout_ms, torch.cuda.current_stream().cuda_stream))
 
     def status(self):
         """Raises if a bounded peer wait gave up since the last check (synchronises the comm stream)."""

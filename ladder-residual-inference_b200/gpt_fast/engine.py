@@ -89,11 +89,26 @@ class Engine:
         self.ops.gateup_swiglu(self.normed if normed is None else normed, w1, self.h, rows, self.ws_ug)
         self.ops.linear(self.h, w2, out, rows, addend=addend)
 
-    def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True, normed=None):
-        """residual += adds (in place), normed = RMSNorm(residual) * weight."""
-        self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps,
-                             self.resid if (write_residual and (add1 is not None or scale != 1.0)) else None,
-                             self.normed if normed is None else normed, rows, scale)
+    def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True, normed=None, ch1=0, ch2=0):
+        """residual += adds (in place), normed = RMSNorm(residual) * weight.  With ch1 / ch2 > 0 the
+        addend is this rank's partial and the sum over ranks is gathered inside the kernel from the
+        message pushed on that channel (the reduction half of the all-reduce)."""
+        res_out = self.resid if (write_residual and (add1 is not None or scale != 1.0)) else None
+        out = self.normed if normed is None else normed
+        if (ch1 and add1 is not None) or (ch2 and add2 is not None):
+            self.comm.add_rmsnorm_gather(self.resid, ch1 if add1 is not None else 0, add1,
+                                         ch2 if add2 is not None else 0, add2, weight, self.cfg.norm_eps, res_out, out,
+                                         rows, scale)
+        else:
+            self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps, res_out, out, rows, scale)
+
+    def _issue(self, buf, rows, channel, split):
+        """Start the all-reduce of a partial: push it (split form, reduced by the consuming norm) or
+        launch the asynchronous all-reduce and return its handle."""
+        if split:
+            self.comm.push(buf, rows, channel)
+            return None
+        return self.comm.all_reduce_async(buf, rows)
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -117,21 +132,23 @@ class Engine:
         if S == 1 and self.overlap_sublayers:
             return self._run_ladder_two_streams(rows, B, S, pos)
         comm, m = self.comm, self.model
+        split = comm.can_split(rows * self.d)
+        ca, cm = (1, 2) if split else (0, 0)
         h_a = h_m = None
         first = True
         for layer in m.layers:
             comm.wait(h_a)
-            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a)
+            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
             self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
-            h_a = comm.all_reduce_async(self.part_a, rows)
+            h_a = self._issue(self.part_a, rows, 1, split)
             comm.wait(h_m)
-            self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m)
+            self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, ch1=cm)
             self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
-            h_m = comm.all_reduce_async(self.part_m, rows)
+            h_m = self._issue(self.part_m, rows, 2, split)
             first = False
         comm.wait(h_a)
         comm.wait(h_m)
-        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False)
+        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False, ch1=ca, ch2=cm)
 
     def _run_ladder_two_streams(self, rows, B, S, pos):
         """Decode form of the ladder schedule.  In a ladder block the MLP of layer i reads the
@@ -144,6 +161,8 @@ class Engine:
         with the side add of layer i ordered after the main add of layer i and before the main add
         of layer i+1 by events."""
         comm, m = self.comm, self.model
+        split = comm.can_split(rows * self.d)
+        ca, cm = (1, 2) if split else (0, 0)
         main = torch.cuda.current_stream()
         side = self.side_stream
         ev = self._events
@@ -156,52 +175,64 @@ class Engine:
             e_attn_add, e_mlp_add = ev[n], ev[n + 1]
             n += 2
             comm.wait(h_a)
-            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a)
+            self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
             e_attn_add.record(main)
             self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
-            h_a = comm.all_reduce_async(self.part_a, rows)
+            h_a = self._issue(self.part_a, rows, 1, split)
             with torch.cuda.stream(side):
                 side.wait_event(e_attn_add)
                 comm.wait(h_m)
-                self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, normed=self.normed_m)
+                self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, normed=self.normed_m,
+                           ch1=cm)
                 e_mlp_add.record(side)
                 self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m,
                           normed=self.normed_m)
-                h_m = comm.all_reduce_async(self.part_m, rows)
+                h_m = self._issue(self.part_m, rows, 2, split)
             main.wait_event(e_mlp_add)  # the next attention add reads the residual the MLP add wrote
             first = False
         ev[n].record(side)
         main.wait_event(ev[n])  # join: the last w2 (and its all-reduce issue) is ordered before the final add
         comm.wait(h_a)
         comm.wait(h_m)
-        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False)
+        self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False, ch1=ca, ch2=cm)
+
+    def _reduce_now(self, buf, rows, channel, split):
+        """All-reduce consumed by the very next norm: pushed (and gathered there) or done in-stream."""
+        if split:
+            self.comm.push(buf, rows, channel)
+        else:
+            self.comm.all_reduce(buf, rows)
 
     def _run_dense(self, rows, B, S, pos):
         comm, m = self.comm, self.model
+        split = comm.can_split(rows * self.d)
+        ca, cm = (1, 2) if split else (0, 0)
         pending = None
         for layer in m.layers:
-            self._norm(layer.attention_norm.weight, rows, add1=pending)
+            self._norm(layer.attention_norm.weight, rows, add1=pending, ch1=cm)
             self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
-            comm.all_reduce(self.part_a, rows)
-            self._norm(layer.ffn_norm.weight, rows, add1=self.part_a)
+            self._reduce_now(self.part_a, rows, 1, split)
+            self._norm(layer.ffn_norm.weight, rows, add1=self.part_a, ch1=ca)
             self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
-            comm.all_reduce(self.part_m, rows)
+            self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
-        self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
+        self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)
 
     def _run_parallel(self, rows, B, S, pos):
         comm, m = self.comm, self.model
+        split = comm.can_split(rows * self.d)
+        cm = 2 if split else 0
         pending = None
         for layer in m.layers:
             att = layer.attention
-            self._norm(layer.attention_norm.weight, rows, add1=pending)
+            self._norm(layer.attention_norm.weight, rows, add1=pending, ch1=cm)
             w = att.wqkv1.weight
             nqkv = att.qkv_rows
             self._attention(att, w[:nqkv], rows, B, S, pos, self.part_a)
             self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a)
-            comm.all_reduce(self.part_m, rows)
+            self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
-        self._norm(m.norm.weight, rows, add1=pending, write_residual=False)
+        self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)
 
     def _run_desync(self, rows, B, S, pos):
         comm, m = self.comm, self.model

@@ -62,8 +62,9 @@ def build(family, cfg, full, dtype, name):
     return model
 
 
-def check_models(comm_name):
+def check_models(comm_name, split=True):
     os.environ["LRI_COMM"] = comm_name
+    os.environ["LRI_SPLIT_AR"] = "1" if split else "0"
     comm_mod.reset_comm()
     gold = gu.load(world)
     for family in gu.FAMILIES:
@@ -95,7 +96,8 @@ def check_models(comm_name):
                     far = gu.rel_err(steps, ref)
                     assert far < 1.5 * gu.rel_err(osteps, ref) + 1e-2, f"{comm_name} {key}: {far:.3e} from the fp32 run"
             model._engine.comm.status()
-    log(f"models ok with comm={comm_name}")
+    os.environ["LRI_SPLIT_AR"] = "1"
+    log(f"models ok with comm={comm_name} split={split}")
 
 
 def check_graph_with_comm():
@@ -162,7 +164,8 @@ def main():
     c = check_p2p_allreduce()
     c.close()
     check_models("nccl")
-    check_models("p2p")
+    check_models("p2p", split=True)    # push after the projection, reduction inside the next add + norm
+    check_models("p2p", split=False)   # stand-alone all-reduce kernel
     check_graph_with_comm()
     check_bounded_wait()
     dist.barrier()
