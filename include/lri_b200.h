@@ -187,11 +187,17 @@ int lri_allreduce(lri_comm* comm, int dtype, const void* in, void* out, int64_t 
  * to this rank's own partial; rank-order fp32 sum, rounded once, bit-identical on all ranks) and,
  * when channel_k == 0, a plain addend pointer or NULL.  No reduce kernel and no stream fork: an
  * all-reduce costs one small push kernel.  A rank must consume message n of a channel before it
- * pushes message n+1 on it (two buffers per channel), which every schedule here does; all ranks
- * push the same sequence.  The consumer's wait is bounded by timeout_ms (status word as above).
+ * pushes message n+1 on it (the consumer advances the channel's epoch; two buffers per channel),
+ * which every schedule here does; all ranks push the same sequence.  The consumer's wait is bounded by timeout_ms (status word as above).
  * Replaces: all_reduce_func + the residual add + RMSNorm that follow it,
- * gpt_fast/gpt_ladder_TP.py:323-356, gpt_fast/gpt_dense_TP.py:281-282. */
+ * gpt_fast/gpt_ladder_TP.py:323-356, gpt_fast/gpt_dense_TP.py:281-282.
+ * lri_linear_push is lri_linear (decode, M <= 8) whose epilogue also pushes: every finished
+ * output pair goes to the peers as an 8-byte {2 elements, epoch} half line, so the transfer
+ * overlaps the tail of the projection and no push kernel is launched (the fused
+ * compute + collective form of the row-parallel projections wo / w2). */
 int64_t lri_comm_push_max_elems(void);
+int lri_linear_push(lri_comm* comm, int channel, int dtype, const void* x, const void* w,
+                    const void* addend, void* y, int64_t M, int N, int K, lri_stream_t stream);
 int lri_comm_push(lri_comm* comm, int channel, int dtype, const void* in, int64_t count,
                   lri_stream_t stream);
 int lri_add_rmsnorm_gather(lri_comm* comm, int dtype, const void* residual, int channel1,

@@ -38,8 +38,9 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
   unsigned int epoch1 = 0, epoch2 = 0;
   unsigned long long t0 = 0;
   if (GATHER) {
-    if (g.s1.enabled) epoch1 = *reinterpret_cast<const volatile unsigned int*>(g.s1.epoch_ptr);
-    if (g.s2.enabled) epoch2 = *reinterpret_cast<const volatile unsigned int*>(g.s2.epoch_ptr);
+    // the message to read is the one after the last consumed one
+    if (g.s1.enabled) epoch1 = *reinterpret_cast<const volatile unsigned int*>(g.s1.epoch_ptr) + 1u;
+    if (g.s2.enabled) epoch2 = *reinterpret_cast<const volatile unsigned int*>(g.s2.epoch_ptr) + 1u;
     t0 = ll_global_ns();
   }
   float vals[kMaxVecPerThread][8];
@@ -82,6 +83,13 @@ add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, c
         vals[i][e] = x[e];
         ss += x[e] * x[e];
       }
+    }
+  }
+  if (GATHER) {
+    __syncthreads();  // every thread of this CTA has finished reading the peers' lines
+    if (threadIdx.x == 0) {
+      if (g.s1.enabled) ll_mark_consumed(g.s1, epoch1);
+      if (g.s2.enabled) ll_mark_consumed(g.s2, epoch2);
     }
   }
   if (normed_out == nullptr) return;

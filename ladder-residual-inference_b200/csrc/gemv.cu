@@ -125,8 +125,23 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
     const int64_t n = static_cast<int64_t>(blockIdx.x) * R + 2 * j;
     T* y = static_cast<T*>(p.y) + static_cast<int64_t>(m) * p.n;
     const T* add = p.addend ? static_cast<const T*>(p.addend) + static_cast<int64_t>(m) * p.n : nullptr;
-    if (n < p.n) y[n] = Num<T>::from_f(add ? v0 + Num<T>::to_f(add[n]) : v0);
-    if (n + 1 < p.n) y[n + 1] = Num<T>::from_f(add ? v1 + Num<T>::to_f(add[n + 1]) : v1);
+    const float o0 = n < p.n ? rnd<T>(add ? v0 + Num<T>::to_f(add[n]) : v0) : 0.f;
+    const float o1 = n + 1 < p.n ? rnd<T>(add ? v1 + Num<T>::to_f(add[n + 1]) : v1) : 0.f;
+    if (n < p.n) y[n] = Num<T>::from_f(o0);
+    if (n + 1 < p.n) y[n + 1] = Num<T>::from_f(o1);
+    if (p.push.enabled && n + 1 < p.n) {
+      // also hand the pair to every peer: 8 bytes {2 elements, epoch}, valid as soon as they land
+      const unsigned int epoch = *reinterpret_cast<const volatile unsigned int*>(p.push.epoch_ptr) + 1u;
+      const size_t off = p.push.region_off +
+                         (static_cast<size_t>(epoch & 1u) * p.push.world + p.push.rank) * p.push.slot_bytes +
+                         static_cast<size_t>((static_cast<int64_t>(m) * p.n + n) >> 1) * 8;
+      const unsigned int data = pack2<T>(o0, o1);
+#pragma unroll 1
+      for (int r = 0; r < p.push.world; ++r)
+        if (r != p.push.rank)
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p.push.inbox[r] + off), "r"(data), "r"(epoch)
+                       : "memory");
+    }
   } else if (EPI == EPI_SWIGLU) {
     const int64_t jj = static_cast<int64_t>(blockIdx.x) * (R / 2) + j;
     if (jj < p.n) static_cast<T*>(p.y)[static_cast<int64_t>(m) * p.n + jj] = swiglu_rounded<T>(v0, v1);

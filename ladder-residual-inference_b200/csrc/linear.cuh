@@ -8,6 +8,18 @@ namespace lri {
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
 constexpr int kGemvMaxRows = 8;
 
+// Producer side of the split all-reduce, fused into the epilogue of a row-parallel projection:
+// every finished output pair is also stored, as an 8-byte half line {2 elements, epoch}, into slot
+// `rank` of every peer's inbox on a push channel.  The epoch is the channel's count of consumed
+// messages plus one; the consumer (the gathering add + RMSNorm) advances the count.
+struct PushArgs {
+  uint8_t* inbox[8];              // every rank's inbox as mapped by this rank
+  const unsigned int* epoch_ptr;  // this rank's counter of consumed messages on the channel
+  size_t region_off;              // offset of the channel's line region inside an inbox
+  int64_t slot_bytes;             // bytes of one (buffer, source rank) slot
+  int world, rank, enabled;
+};
+
 struct LinearParams {
   const void* x;  // [m, k]
   const void* w;  // PLAIN/QKV: [n, k]; SWIGLU: [2n, k] = [up rows | gate rows]
@@ -24,6 +36,7 @@ struct LinearParams {
   int S, n_head, n_kv, head_dim;
   int64_t smax, table_rows;
   int table_gathered;  // rope_table row s belongs to token s (rows already gathered by position)
+  PushArgs push;       // PLAIN epilogue of the SIMT kernel only
 };
 
 // Epilogue of the QKV projection for token row `m` and the adjacent output pair (n, n+1),

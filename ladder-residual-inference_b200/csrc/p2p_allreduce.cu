@@ -15,6 +15,7 @@
 #include <cstddef>
 #include <cstring>
 
+#include "linear.cuh"
 #include "p2p_ll.cuh"
 
 struct lri_comm {
@@ -37,8 +38,8 @@ struct Control {
   unsigned int ticket;  // CTAs retired in the running call
   int status;           // LRI_OK or LRI_ERR_TIMEOUT
   int pad;
-  unsigned int chan_epoch[4];   // per push channel: number of completed pushes
-  unsigned int chan_ticket[4];  // per push channel: CTAs retired in the running push
+  unsigned int chan_epoch[4];   // per push channel: number of messages consumed by this rank
+  unsigned int chan_ticket[4];  // per push channel: consumer CTAs that have finished reading
 };
 
 __host__ __device__ inline size_t data_bytes(int world, int64_t max_bytes) {
@@ -169,9 +170,10 @@ __global__ void __launch_bounds__(kArThreads) allreduce_ll_kernel(const ArParams
   }
 }
 
-// Producer half of the split all-reduce: store this rank's partial as lines into slot `rank` of
-// every peer's region of push channel `ch` (1-based).  The channel's epoch advances when the last
-// CTA retires; the consumer (the gathering add + RMSNorm) reads it from there.
+// Producer half of the split all-reduce as a kernel of its own (used when the projection that
+// produced the partial cannot push from its epilogue): store this rank's partial as lines into
+// slot `rank` of every peer's region of push channel `ch` (1-based).  The epoch is the channel's
+// count of consumed messages plus one; the consumer advances the count.
 __global__ void __launch_bounds__(kArThreads) ll_push_kernel(const ArParams p, int ch) {
   pdl_launch_dependents();
   pdl_wait();  // the partial comes from the preceding kernel
@@ -188,16 +190,6 @@ __global__ void __launch_bounds__(kArThreads) ll_push_kernel(const ArParams p, i
 #pragma unroll 1
     for (int r = 0; r < p.world; ++r)
       if (r != p.rank) st_volatile16(p.inbox[r] + my_slot + u * 16, line);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned int t = atomicAdd(&ctl->chan_ticket[ch], 1u);
-    if (t == gridDim.x - 1) {
-      ctl->chan_ticket[ch] = 0u;
-      __threadfence();
-      *reinterpret_cast<volatile unsigned int*>(&ctl->chan_epoch[ch]) = epoch;
-    }
   }
 }
 
@@ -397,6 +389,31 @@ extern "C" int lri_comm_push(lri_comm* c, int channel, int dtype, const void* in
   return LRI_OK;
 }
 
+// lri_linear with the push fused into the projection's epilogue (decode, M <= 8 rows).
+extern "C" int lri_linear_push(lri_comm* c, int channel, int dtype, const void* x, const void* w, const void* addend,
+                               void* y, int64_t M, int N, int K, lri_stream_t stream) {
+  LRI_REQUIRE(c && x && w && y, LRI_ERR_ARG, "linear_push: NULL argument");
+  LRI_REQUIRE(channel >= 1 && channel <= kPushChannels, LRI_ERR_ARG, "linear_push: channel %d outside 1..%d", channel,
+              kPushChannels);
+  LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "linear_push: dtype %d", dtype);
+  LRI_REQUIRE(M >= 1 && M <= kGemvMaxRows, LRI_ERR_UNSUPPORTED, "linear_push: M=%lld outside 1..%d", (long long)M,
+              kGemvMaxRows);
+  LRI_REQUIRE(N > 0 && N % 8 == 0 && K > 0 && K % 8 == 0 && M * N * 2 <= kLlMaxPayload, LRI_ERR_UNSUPPORTED,
+              "linear_push: N=%d K=%d must be multiples of 8 and M*N*2 <= %lld bytes", N, K, (long long)kLlMaxPayload);
+  LRI_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y), LRI_ERR_ALIGN, "linear_push: pointers must be 16-byte aligned");
+  for (int r = 0; r < c->world; ++r)
+    LRI_REQUIRE(c->peer[r] != nullptr, LRI_ERR_ARG, "linear_push: peer %d is not connected", r);
+  LinearParams p{};
+  p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
+  for (int r = 0; r < c->world; ++r) p.push.inbox[r] = c->peer[r];
+  uint8_t* ctl = c->local + control_offset(c->world, c->max_bytes);
+  p.push.epoch_ptr = reinterpret_cast<const unsigned int*>(ctl + offsetof(Control, chan_epoch)) + channel;
+  p.push.region_off = ll_region(c->world, c->max_bytes, channel);
+  p.push.slot_bytes = kLlSlotBytes;
+  p.push.world = c->world, p.push.rank = c->rank, p.push.enabled = 1;
+  return gemv_launch(dtype, EPI_PLAIN, p, static_cast<cudaStream_t>(stream));
+}
+
 static int fill_source(lri_comm* c, int channel, const void* own, int64_t count, int timeout_ms, LlSource* s) {
   s->enabled = 0;
   if (channel <= 0) return LRI_OK;
@@ -408,7 +425,8 @@ static int fill_source(lri_comm* c, int channel, const void* own, int64_t count,
               (long long)count);
   uint8_t* ctl = c->local + control_offset(c->world, c->max_bytes);
   s->region = c->local + ll_region(c->world, c->max_bytes, channel);
-  s->epoch_ptr = reinterpret_cast<const unsigned int*>(ctl + offsetof(Control, chan_epoch)) + channel;
+  s->epoch_ptr = reinterpret_cast<unsigned int*>(ctl + offsetof(Control, chan_epoch)) + channel;
+  s->ticket_ptr = reinterpret_cast<unsigned int*>(ctl + offsetof(Control, chan_ticket)) + channel;
   s->status_ptr = reinterpret_cast<int*>(ctl + offsetof(Control, status));
   s->own = own;
   s->slot_bytes = kLlSlotBytes;

@@ -13,7 +13,8 @@ namespace lri {
 
 struct LlSource {
   const uint8_t* region;          // this rank's inbox: start of the channel's line region (both buffers)
-  const unsigned int* epoch_ptr;  // the channel's epoch counter in this rank's memory
+  unsigned int* epoch_ptr;        // the channel's counter of consumed messages (this rank's memory)
+  unsigned int* ticket_ptr;       // arrival counter of the consumer's CTAs (self-resetting)
   int* status_ptr;                // receives LRI_ERR_TIMEOUT when a bounded poll gives up
   const void* own;                // this rank's own partial (same layout as the message)
   int64_t slot_bytes;             // bytes of one (buffer, source rank) slot
@@ -45,7 +46,7 @@ __device__ __forceinline__ unsigned long long ll_global_ns() {
 // kernel would have written).  The wait is bounded; on expiry the status word is set and the
 // values seen so far are used.
 template <typename T>
-__device__ __forceinline__ void ll_gather8(const LlSource& s, unsigned int epoch, int64_t elem, float (&out)[8],
+__device__ __noinline__ void ll_gather8(const LlSource& s, unsigned int epoch, int64_t elem, float (&out)[8],
                                            unsigned long long t0) {
   const int buf = epoch & 1u;
   const uint8_t* base = s.region + static_cast<size_t>(buf) * s.world * s.slot_bytes + (elem >> 2) * 16;
@@ -84,6 +85,18 @@ __device__ __forceinline__ void ll_gather8(const LlSource& s, unsigned int epoch
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) out[e] = rnd<T>(acc[e]);
+}
+
+// After a consumer kernel has read everything it needs from message `epoch`: the last of its
+// CTAs marks the message as consumed (thread 0 of every CTA calls this after a __syncthreads()).
+__device__ __forceinline__ void ll_mark_consumed(const LlSource& s, unsigned int epoch) {
+  __threadfence();
+  const unsigned int t = atomicAdd(s.ticket_ptr, 1u);
+  if (t == gridDim.x - 1) {
+    *s.ticket_ptr = 0u;
+    __threadfence();
+    *reinterpret_cast<volatile unsigned int*>(s.epoch_ptr) = epoch;
+  }
 }
 
 // defined in add_rmsnorm.cu: the fused add + RMSNorm whose addends may be gathered from peers

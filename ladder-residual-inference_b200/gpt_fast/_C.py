@@ -54,6 +54,8 @@ _SIGNATURES = {
     "lri_comm_connect": (c_int, [c_void_p, ctypes.c_char_p]),
     "lri_allreduce": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "lri_comm_push_max_elems": (c_int64, []),
+    "lri_linear_push": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                c_void_p]),
     "lri_comm_push": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "lri_add_rmsnorm_gather": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p,
                                        c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),

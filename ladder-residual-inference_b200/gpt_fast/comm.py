@@ -29,7 +29,7 @@ class NoComm:
     rank = 0
     name = "none"
 
-    def can_split(self, count):
+    def can_split(self, count, rows=1, hidden=False):
         return False
 
     def all_reduce_async(self, t, rows=None):
@@ -48,7 +48,7 @@ class NoComm:
 class TorchComm:
     name = "torch.distributed"
 
-    def can_split(self, count):
+    def can_split(self, count, rows=1, hidden=False):
         return False
 
     def __init__(self):
@@ -117,7 +117,7 @@ class P2PComm:
         self._done = [torch.cuda.Event() for _ in range(4)]
         self._n = 0
         self._push_max = _C.lib.lri_comm_push_max_elems()
-        self.split_enabled = os.environ.get("LRI_SPLIT_AR", "1") != "0"
+        self.split_mode = os.environ.get("LRI_SPLIT_AR", "auto")
 
     def all_reduce_async(self, t, rows=None):
         if rows is not None and rows != t.shape[0]:
@@ -156,9 +156,25 @@ class P2PComm:
                                                  count, self.timeout_ms, torch.cuda.current_stream().cuda_stream))
 
     # ---- split all-reduce: push now, reduce inside the consuming add + RMSNorm ----------------
-    def can_split(self, count):
-        """True when a message of `count` elements can take the push / gather path."""
-        return self.split_enabled and count % 8 == 0 and count <= self._push_max
+    def can_split(self, count, rows=1, hidden=False):
+        """True when the partial of a row-parallel projection takes the split path: pushed from the
+        projection's epilogue and reduced inside the consuming add + RMSNorm.  Used for single-row
+        decode steps, where the fused push exists; larger steps use the all-reduce kernel.
+        `hidden` says that the schedule consumes the sum a sublayer later (ladder): there the
+        stand-alone kernel on the communication stream is already off the critical path and
+        measured slightly faster (2 GPUs), so LRI_SPLIT_AR=auto keeps it; =1 forces the split
+        path everywhere, =0 turns it off."""
+        if self.split_mode == "0" or (self.split_mode == "auto" and hidden):
+            return False
+        return rows == 1 and count % 8 == 0 and count <= self._push_max
+
+    def linear_push(self, x, w, out, rows, channel, addend=None):
+        """out = x W^T (+ addend) with the result also pushed to the peers on `channel`."""
+        C = self._C
+        n, k = w.shape
+        C.check(C.lib.lri_linear_push(self.handle, channel, C.dtype_code(x.dtype), x.data_ptr(), w.data_ptr(),
+                                      C.ptr(addend), out.data_ptr(), rows, n, k,
+                                      torch.cuda.current_stream().cuda_stream))
 
     def push(self, t, rows, channel):
         """Store rows [0, rows) of `t` into every peer's inbox on push channel 1 or 2 (current stream)."""

@@ -77,17 +77,24 @@ class Engine:
         self.ready = True
 
     # ------------------------------------------------------------------------------------------
-    def _attention(self, att, w_qkv, rows, B, S, pos, out):
+    def _attention(self, att, w_qkv, rows, B, S, pos, out, push=0):
+        """push > 0: the output projection also pushes its partial to the peers on that channel."""
         ops = self.ops
         kc, vc = att.kv_cache.k_cache, att.kv_cache.v_cache
         ops.qkv_rope_kvcache(self.normed, w_qkv, self.model.freqs_cis, False, pos, self.q, kc, vc, B, S, self.nh,
                              self.nkv, self.hd, self.ws_qkv)
         ops.attention(self.q, kc, vc, pos, self.y, B, S, self.nh, self.nkv, self.hd, self.scratch, self._splits)
-        ops.linear(self.y, att.wo.weight, out, rows)
+        if push:
+            self.comm.linear_push(self.y, att.wo.weight, out, rows, push)
+        else:
+            ops.linear(self.y, att.wo.weight, out, rows)
 
-    def _mlp(self, w1, w2, rows, out, addend=None, normed=None):
+    def _mlp(self, w1, w2, rows, out, addend=None, normed=None, push=0):
         self.ops.gateup_swiglu(self.normed if normed is None else normed, w1, self.h, rows, self.ws_ug)
-        self.ops.linear(self.h, w2, out, rows, addend=addend)
+        if push:
+            self.comm.linear_push(self.h, w2, out, rows, push, addend=addend)
+        else:
+            self.ops.linear(self.h, w2, out, rows, addend=addend)
 
     def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True, normed=None, ch1=0, ch2=0):
         """residual += adds (in place), normed = RMSNorm(residual) * weight.  With ch1 / ch2 > 0 the
@@ -103,10 +110,9 @@ class Engine:
             self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps, res_out, out, rows, scale)
 
     def _issue(self, buf, rows, channel, split):
-        """Start the all-reduce of a partial: push it (split form, reduced by the consuming norm) or
-        launch the asynchronous all-reduce and return its handle."""
+        """Start the all-reduce of a partial.  Split form: the projection has pushed it already and the
+        consuming norm reduces it, nothing to do; else launch the asynchronous all-reduce."""
         if split:
-            self.comm.push(buf, rows, channel)
             return None
         return self.comm.all_reduce_async(buf, rows)
 
@@ -132,18 +138,18 @@ class Engine:
         if S == 1 and self.overlap_sublayers:
             return self._run_ladder_two_streams(rows, B, S, pos)
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d)
+        split = comm.can_split(rows * self.d, rows, hidden=True)
         ca, cm = (1, 2) if split else (0, 0)
         h_a = h_m = None
         first = True
         for layer in m.layers:
             comm.wait(h_a)
             self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
             h_a = self._issue(self.part_a, rows, 1, split)
             comm.wait(h_m)
             self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, ch1=cm)
-            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=cm)
             h_m = self._issue(self.part_m, rows, 2, split)
             first = False
         comm.wait(h_a)
@@ -161,7 +167,7 @@ class Engine:
         with the side add of layer i ordered after the main add of layer i and before the main add
         of layer i+1 by events."""
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d)
+        split = comm.can_split(rows * self.d, rows, hidden=True)
         ca, cm = (1, 2) if split else (0, 0)
         main = torch.cuda.current_stream()
         side = self.side_stream
@@ -177,7 +183,7 @@ class Engine:
             comm.wait(h_a)
             self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
             e_attn_add.record(main)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
             h_a = self._issue(self.part_a, rows, 1, split)
             with torch.cuda.stream(side):
                 side.wait_event(e_attn_add)
@@ -186,7 +192,7 @@ class Engine:
                            ch1=cm)
                 e_mlp_add.record(side)
                 self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m,
-                          normed=self.normed_m)
+                          normed=self.normed_m, push=cm)
                 h_m = self._issue(self.part_m, rows, 2, split)
             main.wait_event(e_mlp_add)  # the next attention add reads the residual the MLP add wrote
             first = False
@@ -198,29 +204,27 @@ class Engine:
 
     def _reduce_now(self, buf, rows, channel, split):
         """All-reduce consumed by the very next norm: pushed (and gathered there) or done in-stream."""
-        if split:
-            self.comm.push(buf, rows, channel)
-        else:
+        if not split:
             self.comm.all_reduce(buf, rows)
 
     def _run_dense(self, rows, B, S, pos):
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d)
+        split = comm.can_split(rows * self.d, rows)
         ca, cm = (1, 2) if split else (0, 0)
         pending = None
         for layer in m.layers:
             self._norm(layer.attention_norm.weight, rows, add1=pending, ch1=cm)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
             self._reduce_now(self.part_a, rows, 1, split)
             self._norm(layer.ffn_norm.weight, rows, add1=self.part_a, ch1=ca)
-            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=cm)
             self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)
 
     def _run_parallel(self, rows, B, S, pos):
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d)
+        split = comm.can_split(rows * self.d, rows)
         cm = 2 if split else 0
         pending = None
         for layer in m.layers:
@@ -229,7 +233,7 @@ class Engine:
             w = att.wqkv1.weight
             nqkv = att.qkv_rows
             self._attention(att, w[:nqkv], rows, B, S, pos, self.part_a)
-            self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a)
+            self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a, push=cm)
             self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)
