@@ -79,10 +79,15 @@ int lri_embedding(int dtype, const void* table, const void* idx, int idx_is_i64,
 
 /* ---- F5 / F7: linear layer y = x W^T (+ addend) ------------------------------------------
  * x [M, K], w [N, K], y [M, N].  addend (may be NULL) is added after y's own rounding and the
- * sum rounded again (the parallel block's `w2(...) + y`, gpt_fast/utils.py:385).  M <= 16 runs
- * the weight-streaming kernels (SIMT for one row, mma.sync for 2..16); larger M the tcgen05 GEMM.  workspace is unused today (pass
- * NULL, 0).  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
+ * sum rounded again (the parallel block's `w2(...) + y`, gpt_fast/utils.py:385).  M <= 8 runs
+ * the weight-streaming kernels (SIMT for one row, mma.sync for 2..8); larger M the tcgen05 GEMM.
+ * For 8 < M <= 64 a workspace of lri_linear_workspace_bytes(M, N) bytes (16-byte aligned) lets
+ * the tcgen05 GEMM cut K into slices so that a narrow projection still occupies every SM (fp32
+ * partial sums in the workspace, summed by a second kernel that also applies the addend); with
+ * NULL / a smaller workspace fewer or no slices are used.  Two calls that may run at the same
+ * time on different streams need different workspaces.  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
  * 258, 384-385 and gpt_fast/gpt_ladder_TP.py:283. */
+size_t lri_linear_workspace_bytes(int64_t M, int N);
 int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M,
                int N, int K, void* workspace, size_t workspace_bytes, lri_stream_t stream);
 
@@ -95,7 +100,7 @@ int lri_linear(int dtype, const void* x, const void* w, const void* addend, void
  * written to k_cache / v_cache [B_max, n_kv, smax, head_dim] at [b, h, input_pos[s], :].
  * Rotation is over adjacent pairs in fp32 from the rounded projection, as the reference does.
  * A position outside [0, min(smax, table_rows)) is skipped (nothing is written for it).
- * M = B*S > 16 needs workspace of lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) bytes.
+ * M = B*S > 8 needs workspace of lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) bytes.
  * Replaces: gpt_fast/utils.py:187-198 (wqkv, split, apply_rotary_emb) and KVCache.update
  * utils.py:50-59, 249-250. */
 size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim);
@@ -107,7 +112,7 @@ int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void*
 
 /* ---- F6: gate/up projection + SwiGLU -----------------------------------------------------
  * w1 [2*I, K] with rows [up (I rows) | gate (I rows)]; h[m, j] = round(silu(gate_j)) * up_j.
- * M > 16 needs workspace of lri_gateup_workspace_bytes(M, I) bytes.
+ * M > 8 needs workspace of lri_gateup_workspace_bytes(M, I) bytes.
  * Replaces: FeedForward.forward's w1 / chunk / silu*mul, gpt_fast/utils.py:145-148 (and the
  * u, g part of FuseAttentionMLP, utils.py:311-313, 385). */
 size_t lri_gateup_workspace_bytes(int64_t M, int I);

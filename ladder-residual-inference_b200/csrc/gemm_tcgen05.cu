@@ -1,11 +1,13 @@
 // tcgen05 GEMM for sm_100a:  C[m, n] = sum_k A[m, k] * W[n, k]   (both operands K-major).
 //
-// One CTA per 128 x BN output tile.  Warp 0 is the TMA producer, warp 1 allocates TMEM and
-// issues tcgen05.mma (one elected thread), warps 2-5 are the epilogue (each reads its own
-// 32-lane quarter of TMEM with tcgen05.ld and stores C).  Operand tiles are 64 K-elements
-// wide (128 bytes per row) and land in shared memory through plain single-CTA TMA loads in the
-// 128-byte swizzle, which is also the layout the shared-memory matrix descriptors name.  A
-// ring of mbarrier pairs (full / empty) pipelines the K loop; tcgen05.commit releases a stage.
+// Persistent CTAs (one per SM) work through 128 x BN output tiles.  Warp 0 is the TMA producer,
+// warp 1 allocates TMEM and issues tcgen05.mma (one elected thread), warps 2-5 are the epilogue
+// (each reads its own 32-lane quarter of TMEM with tcgen05.ld and stores C).  Operand tiles are
+// 64 K-elements wide (128 bytes per row) and land in shared memory through plain single-CTA TMA
+// loads in the 128-byte swizzle, which is also the layout the shared-memory matrix descriptors
+// name.  A ring of mbarrier pairs (full / empty) pipelines the K loop and keeps running from one
+// tile to the next; tcgen05.commit releases a stage.  Two accumulator buffers in TMEM let the
+// epilogue of one tile overlap the main loop of the next.
 //
 // The 128-row operand of the instruction is the activation tile for prefill-sized m; for
 // m <= 64 the operands are swapped (weights take the 128 rows, tokens the N side) so that
@@ -14,6 +16,8 @@
 // Every wait on an mbarrier is bounded: when the poll budget runs out the kernel records an
 // error in a device status word, stops waiting everywhere, frees its TMEM and returns.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include <type_traits>
 
@@ -110,33 +114,65 @@ struct GemmShape {
   int m, n, k;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// One unit of work of a persistent CTA: an output tile and a slice of K.
+struct WorkItem {
+  int tile_p, tile_q, z, kt_begin, num_kt;
+};
+struct GemmGrid {
+  int tiles_p, tiles_q, splits;
+};
+__device__ __forceinline__ WorkItem work_item(int item, const GemmGrid& g, int total_kt) {
+  WorkItem w;
+  const int per_slice = g.tiles_p * g.tiles_q;
+  w.z = item / per_slice;
+  const int rem = item - w.z * per_slice;
+  w.tile_p = rem / g.tiles_q;  // neighbouring CTAs share the 128-row operand tile and stream different Q tiles
+  w.tile_q = rem - w.tile_p * g.tiles_q;
+  // slice z owns a contiguous range of K tiles, never empty (the host keeps splits <= number of K tiles)
+  w.kt_begin = static_cast<int>(static_cast<int64_t>(total_kt) * w.z / g.splits);
+  w.num_kt = static_cast<int>(static_cast<int64_t>(total_kt) * (w.z + 1) / g.splits) - w.kt_begin;
+  return w;
+}
+
 // P = operand with 128 rows per tile, Q = operand with BN rows per tile.
 // SWAP == false: P = A (tokens), Q = W;  D[i, j] -> C[tile_p*128 + i, tile_q*BN + j]
 // SWAP == true : P = W,          Q = A;  D[i, j] -> C[tile_q*BN + j, tile_p*128 + i]
+// With `partial` set (SWAP only) slice z of K writes fp32 partial[z][token][n] instead of C.
+//
+// The kernel is persistent: CTA b works through items b, b + gridDim.x, ...  The shared-memory
+// ring keeps running across items (the producer is already fetching the next item's operands
+// while the last MMAs of the current one execute) and the accumulator is double-buffered in
+// TMEM, so the epilogue of item i overlaps the main loop of item i + 1.
 template <typename T, int BN, bool SWAP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
-                    T* __restrict__ c, GemmShape shape, int stages) {
+                    T* __restrict__ c, float* __restrict__ partial, GemmShape shape, GemmGrid grid, int stages,
+                    int rotate_k) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t kTileP = kBM * kBK * 2;
   constexpr uint32_t kTileQ = BN * kBK * 2;
   constexpr uint32_t kStageBytes = kTileP + kTileQ;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;  // TMEM columns of one accumulator buffer
+  constexpr uint32_t kTmemCols = 2 * kAccCols;      // a power of two between 64 and 512
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-  __shared__ uint64_t bars[2 * 8 + 1];
+  __shared__ uint64_t bars[2 * 8 + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile_q = blockIdx.x;
-  const int tile_p = blockIdx.y;
-  const int num_kt = (shape.k + kBK - 1) / kBK;
+  const int total_kt = (shape.k + kBK - 1) / kBK;
+  const int items = grid.tiles_p * grid.tiles_q * grid.splits;
 
   const uint32_t full0 = smem_u32(&bars[0]);
   const uint32_t empty0 = smem_u32(&bars[8]);
-  const uint32_t accum_bar = smem_u32(&bars[16]);
+  const uint32_t acc_full0 = smem_u32(&bars[16]);   // MMA -> epilogue, one per accumulator buffer
+  const uint32_t acc_empty0 = smem_u32(&bars[18]);  // epilogue -> MMA
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -144,7 +180,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full0 + 8 * a, 1);
+      mbar_init(acc_empty0 + 8 * a, 128);  // every epilogue thread arrives
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -158,18 +197,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // everything above overlaps the tail of the preceding kernel when launched as its programmatic dependent
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < num_kt; ++kt) {
-        const int s = kt % stages;
-        const uint32_t round = static_cast<uint32_t>(kt / stages);
-        // a fresh barrier passes a wait on parity 1, so the first round does not block
-        if (!mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, &abort_flag, 1)) break;
-        mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        const uint32_t dst = base + s * kStageBytes;
-        tma_load_2d(dst, &tmap_p, full0 + 8 * s, kt * kBK, tile_p * kBM);
-        tma_load_2d(dst + kTileP, &tmap_q, full0 + 8 * s, kt * kBK, tile_q * BN);
+      uint32_t g = 0;  // K tiles loaded so far, over all items: position in the ring
+      bool ok = true;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const WorkItem w = work_item(item, grid, total_kt);
+        const int rot = rotate_k ? item % w.num_kt : 0;
+        for (int kt = 0; kt < w.num_kt; ++kt, ++g) {
+          const uint32_t s = g % static_cast<uint32_t>(stages);
+          const uint32_t round = g / static_cast<uint32_t>(stages);
+          // a fresh barrier passes a wait on parity 1, so the first round does not block
+          ok = mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, &abort_flag, 1);
+          if (!ok) break;
+          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          const uint32_t dst = base + s * kStageBytes;
+          // optional: items walk their K range from different starting points (the sum does not
+          // care about the order)
+          int kr = kt + rot;
+          kr = kr >= w.num_kt ? kr - w.num_kt : kr;
+          const int kx = (w.kt_begin + kr) * kBK;
+          tma_load_2d(dst, &tmap_p, full0 + 8 * s, kx, w.tile_p * kBM);
+          tma_load_2d(dst + kTileP, &tmap_q, full0 + 8 * s, kx, w.tile_q * BN);
+        }
       }
     }
   } else if (warp == 1) {
@@ -178,42 +232,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
       constexpr uint32_t kFmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       constexpr uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                  (static_cast<uint32_t>(kBM >> 4) << 24);
+      uint32_t g = 0;
       bool ok = true;
-      for (int kt = 0; kt < num_kt && ok; ++kt) {
-        const int s = kt % stages;
-        const uint32_t round = static_cast<uint32_t>(kt / stages);
-        ok = mbar_wait(full0 + 8 * s, round & 1u, &abort_flag, 2);
+      int it = 0;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
+        const WorkItem w = work_item(item, grid, total_kt);
+        const uint32_t a = it & 1;
+        const uint32_t use = static_cast<uint32_t>(it) >> 1;
+        // the epilogue must have drained this accumulator buffer (its first use does not block)
+        ok = mbar_wait(acc_empty0 + 8 * a, (use & 1u) ^ 1u, &abort_flag, 4);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t pa = base + s * kStageBytes;
-        const uint64_t pdesc = smem_desc_sw128(pa);
-        const uint64_t qdesc = smem_desc_sw128(pa + kTileP);
+        const uint32_t d_tmem = tmem_base + a * kAccCols;
+        for (int kt = 0; kt < w.num_kt; ++kt, ++g) {
+          const uint32_t s = g % static_cast<uint32_t>(stages);
+          const uint32_t round = g / static_cast<uint32_t>(stages);
+          ok = mbar_wait(full0 + 8 * s, round & 1u, &abort_flag, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t pa = base + s * kStageBytes;
+          const uint64_t pdesc = smem_desc_sw128(pa);
+          const uint64_t qdesc = smem_desc_sw128(pa + kTileP);
 #pragma unroll
-        for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-          // 16 K-elements = 32 bytes further along the swizzled row: +2 in 16-byte units
-          umma_f16(tmem_base, pdesc + 2 * kk, qdesc + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            // 16 K-elements = 32 bytes further along the swizzled row: +2 in 16-byte units
+            umma_f16(d_tmem, pdesc + 2 * kk, qdesc + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
         }
-        umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+        if (ok) umma_commit(acc_full0 + 8 * a);  // arrives when every MMA issued so far has completed
       }
-      umma_commit(accum_bar);  // arrives when every MMA issued so far has completed
     }
   } else {
     const int quarter = warp & 3;  // the TMEM lanes a warp may read are fixed by warp id mod 4
-    const bool ok = mbar_wait(accum_bar, 0, &abort_flag, 3);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const int i = quarter * 32 + lane;  // row of D held by this thread
+    const int i = quarter * 32 + lane;  // row of D held by this thread
+    int it = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
+      const WorkItem w = work_item(item, grid, total_kt);
+      const uint32_t a = it & 1;
+      const uint32_t use = static_cast<uint32_t>(it) >> 1;
+      if (!mbar_wait(acc_full0 + 8 * a, use & 1u, &abort_flag, 3)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + cc;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kAccCols + cc;
         tmem_ld32(taddr, r);  // BN == 16: only the first 16 columns are valid (32 are allocated)
+        constexpr int kValid = BN < 32 ? BN : 32;
         if (!SWAP) {
-          const int64_t row = static_cast<int64_t>(tile_p) * kBM + i;
-          const int64_t col0 = static_cast<int64_t>(tile_q) * BN + cc;
+          const int64_t row = static_cast<int64_t>(w.tile_p) * kBM + i;
+          const int64_t col0 = static_cast<int64_t>(w.tile_q) * BN + cc;
           if (row < shape.m) {
             T* dst = c + row * shape.n + col0;
-            constexpr int kValid = BN < 32 ? BN : 32;
             if (col0 + kValid <= shape.n) {
 #pragma unroll
               for (int v = 0; v < kValid / 8; ++v) {
@@ -229,16 +299,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
             }
           }
         } else {
-          const int64_t n = static_cast<int64_t>(tile_p) * kBM + i;
-          const int64_t tok0 = static_cast<int64_t>(tile_q) * BN + cc;
-          constexpr int kValid = BN < 32 ? BN : 32;
+          const int64_t n = static_cast<int64_t>(w.tile_p) * kBM + i;
+          const int64_t tok0 = static_cast<int64_t>(w.tile_q) * BN + cc;
           if (n < shape.n) {
+            if (partial != nullptr) {
+              float* dst = partial + static_cast<int64_t>(w.z) * shape.m * shape.n + n;
 #pragma unroll
-            for (int e = 0; e < kValid; ++e)
-              if (tok0 + e < shape.m) c[(tok0 + e) * shape.n + n] = Num<T>::from_f(__uint_as_float(r[e]));
+              for (int e = 0; e < kValid; ++e)
+                if (tok0 + e < shape.m) dst[(tok0 + e) * shape.n] = __uint_as_float(r[e]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < kValid; ++e)
+                if (tok0 + e < shape.m) c[(tok0 + e) * shape.n + n] = Num<T>::from_f(__uint_as_float(r[e]));
+            }
           }
         }
       }
+      // this thread's reads of the buffer are complete (tcgen05.wait::ld in tmem_ld32): hand it back
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(acc_empty0 + 8 * a);
     }
   }
 
@@ -286,8 +365,30 @@ int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int64_
   return LRI_OK;
 }
 
+// LRI_GEMM_ROTATE_K=1 makes work items start their walk over K at different tiles (tuning knob;
+// measured neutral to slightly slower on B200, so off by default)
+int rotate_k() {
+  static const int on = [] {
+    const char* e = getenv("LRI_GEMM_ROTATE_K");
+    return (e && atoi(e) == 1) ? 1 : 0;
+  }();
+  return on;
+}
+
+int sm_count() {
+  static const int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      v = 148;
+    return v;
+  }();
+  return n;
+}
+
 template <typename T, int BN, bool SWAP>
-int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
+int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st,
+                float* partial = nullptr, int splits = 1) {
   CUtensorMap tp, tq;
   const void* p_ptr = SWAP ? w : a;
   const void* q_ptr = SWAP ? a : w;
@@ -307,18 +408,27 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
     LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
     attr_set = true;
   }
-  dim3 grid(static_cast<unsigned>((q_rows + BN - 1) / BN), static_cast<unsigned>((p_rows + kBM - 1) / kBM));
+  const int total_kt = (k + kBK - 1) / kBK;
+  splits = splits < 1 ? 1 : (splits > total_kt ? total_kt : splits);
+  if (!SWAP || partial == nullptr) splits = 1;
+  const int64_t tiles_p = (p_rows + kBM - 1) / kBM, tiles_q = (q_rows + BN - 1) / BN;
+  const int64_t items = tiles_p * tiles_q * splits;
+  if (items >= (1ll << 31)) return fail(LRI_ERR_UNSUPPORTED, "gemm: %lld output tiles", (long long)items);
+  GemmGrid grid{static_cast<int>(tiles_p), static_cast<int>(tiles_q), splits};
   GemmShape shape{static_cast<int>(m), n, k};
-  kern<<<grid, kGemmThreads, smem, st>>>(tp, tq, static_cast<T*>(c), shape, stages);
+  const int ctas = static_cast<int>(items < sm_count() ? items : sm_count());
+  LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tp, tq,
+                      static_cast<T*>(c), partial, shape, grid, stages, rotate_k()));
   LRI_LAUNCH_CHECK("gemm_tcgen05_kernel");
   return LRI_OK;
 }
 
 template <typename T>
-int launch_typed(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
-  if (m <= 16) return launch_tile<T, 16, true>(dtype, a, w, c, m, n, k, st);
-  if (m <= 32) return launch_tile<T, 32, true>(dtype, a, w, c, m, n, k, st);
-  if (m <= 64) return launch_tile<T, 64, true>(dtype, a, w, c, m, n, k, st);
+int launch_typed(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st,
+                 float* partial = nullptr, int splits = 1) {
+  if (m <= 16) return launch_tile<T, 16, true>(dtype, a, w, c, m, n, k, st, partial, splits);
+  if (m <= 32) return launch_tile<T, 32, true>(dtype, a, w, c, m, n, k, st, partial, splits);
+  if (m <= 64) return launch_tile<T, 64, true>(dtype, a, w, c, m, n, k, st, partial, splits);
   // prefill: pick the N tile that leaves fewer idle SMs in the last wave
   int sms = 148;
   const int64_t mt = (m + kBM - 1) / kBM;
@@ -338,6 +448,36 @@ bool gemm_tcgen05_supports(int64_t m, int n, int k) {
 int gemm_tcgen05_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
   return dtype == LRI_BF16 ? launch_typed<__nv_bfloat16>(dtype, a, w, c, m, n, k, st)
                            : launch_typed<__half>(dtype, a, w, c, m, n, k, st);
+}
+
+// Small-M (<= 64 token rows) weight-streaming form: W is the 128-row operand, K is cut into
+// `splits` slices, slice z writes fp32 partial[z][m][n]; the caller sums the slices in its epilogue.
+int gemm_tcgen05_splitk_launch(int dtype, const void* a, const void* w, float* partial, int64_t m, int n, int k,
+                               int splits, cudaStream_t st) {
+  if (m > 64 || partial == nullptr) return fail(LRI_ERR_ARG, "gemm split-K: m=%lld must be <= 64", (long long)m);
+  return dtype == LRI_BF16 ? launch_typed<__nv_bfloat16>(dtype, a, w, nullptr, m, n, k, st, partial, splits)
+                           : launch_typed<__half>(dtype, a, w, nullptr, m, n, k, st, partial, splits);
+}
+
+// Number of K slices for the small-M form: fill the 148 SMs (one CTA each) with as little idle
+// tail as possible while every slice keeps at least 8 K tiles to amortise the pipeline fill.
+int gemm_tcgen05_choose_splits(int n, int k) {
+  const int64_t tiles = (n + kBM - 1) / kBM;
+  const int total_kt = (k + kBK - 1) / kBK;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= kMaxSplitK; ++s) {
+    if (s > 1 && total_kt / s < 8) break;
+    const int64_t ctas = tiles * s;
+    const int64_t waves = (ctas + 147) / 148;
+    // idle tail of the last wave, plus a small charge per slice for the fp32 partials
+    const double eff = static_cast<double>(ctas) / (148.0 * waves) - 0.01 * (s - 1);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
 }
 
 int gemm_tcgen05_status_read_and_clear(int* status_out) {

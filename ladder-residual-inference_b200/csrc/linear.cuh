@@ -93,6 +93,17 @@ bool prefer_simt_gemv();
 // C[m, n] = A[m, k] * W[n, k]^T, C in `dtype`, any m.  backend: lri_gemm_backend.
 int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);
 
+// Small-batch decode above the streaming kernels (up to kSplitKMaxRows token rows): the tcgen05
+// GEMM with the weights as the 128-row operand and K cut into slices, fp32 partials in a
+// workspace, then one kernel that sums the slices and runs the projection's epilogue.
+constexpr int kMaxSplitK = 8;
+constexpr int kSplitKMaxRows = 64;
+int gemm_tcgen05_choose_splits(int n, int k);
+int gemm_tcgen05_splitk_launch(int dtype, const void* a, const void* w, float* partial, int64_t m, int n, int k,
+                               int splits, cudaStream_t st);
+// p.m rows, p.n outputs (SWIGLU: partial has 2 * p.n columns); partial = [splits, p.m, columns] fp32
+int splitk_finish_launch(int dtype, int epi, const float* partial, int splits, const LinearParams& p, cudaStream_t st);
+
 // elementwise epilogues used after the GEMM on the prefill path
 int swiglu_rows_launch(int dtype, const void* ug /*[m, 2n]*/, void* h /*[m, n]*/, int64_t m, int n, cudaStream_t st);
 int qkv_scatter_launch(int dtype, const void* qkv /*[m, (nh+2nkv)*hd]*/, const LinearParams& p, cudaStream_t st);

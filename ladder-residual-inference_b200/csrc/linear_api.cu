@@ -46,11 +46,12 @@ bool pdl_enabled() {
   return on;
 }
 // Token rows up to which the weight-streaming kernels (no workspace) are used; more rows go to the
-// tcgen05 GEMM.  LRI_STREAM_ROWS=1..16 lowers the limit (tuning knob).
+// tcgen05 GEMM (measured cross-over on B200: the streaming kernels win up to 8 rows).
+// LRI_STREAM_ROWS=1..16 moves the limit (tuning knob).
 int streaming_rows() {
   static const int rows = [] {
     const char* e = getenv("LRI_STREAM_ROWS");
-    const int v = e ? atoi(e) : kGemvMmaMaxRows;
+    const int v = e ? atoi(e) : 8;
     return v < 1 ? 1 : (v > kGemvMmaMaxRows ? kGemvMmaMaxRows : v);
   }();
   return rows;
@@ -163,6 +164,64 @@ __global__ void __launch_bounds__(256) add_rows_kernel(T* __restrict__ y, const 
   reinterpret_cast<uint4*>(y)[i] = pack8<T>(a);
 }
 
+// Sum of the K slices of a split-K GEMM followed by the projection's epilogue; one thread per
+// token row and output pair (PLAIN / QKV: columns 2j, 2j+1; SWIGLU: columns j and n + j).
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const float* __restrict__ partial, int splits,
+                                                            const LinearParams p) {
+  const int64_t pairs = EPI == EPI_SWIGLU ? p.n : (p.n >> 1);
+  const int64_t cols = EPI == EPI_SWIGLU ? 2 * static_cast<int64_t>(p.n) : p.n;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
+  if (idx >= pairs * p.m) return;
+  const int64_t m = idx / pairs;
+  const int64_t j = idx - m * pairs;
+  float s0 = 0.f, s1 = 0.f;
+  const float* src = partial + m * cols;
+  const int64_t slice = static_cast<int64_t>(p.m) * cols;
+  if (EPI == EPI_SWIGLU) {
+    for (int z = 0; z < splits; ++z) {
+      s0 += src[z * slice + j];
+      s1 += src[z * slice + p.n + j];
+    }
+    static_cast<T*>(p.y)[m * p.n + j] = swiglu_rounded<T>(rnd<T>(s0), rnd<T>(s1));
+    return;
+  }
+  for (int z = 0; z < splits; ++z) {
+    const float2 v = *reinterpret_cast<const float2*>(src + z * slice + 2 * j);
+    s0 += v.x;
+    s1 += v.y;
+  }
+  const float v0 = rnd<T>(s0), v1 = rnd<T>(s1);
+  const int64_t n = 2 * j;
+  if (EPI == EPI_PLAIN) {
+    float o0 = v0, o1 = v1;
+    if (p.addend) {
+      const T* add = static_cast<const T*>(p.addend) + m * p.n + n;
+      o0 = rnd<T>(v0 + Num<T>::to_f(add[0]));
+      o1 = rnd<T>(v1 + Num<T>::to_f(add[1]));
+    }
+    *reinterpret_cast<uint32_t*>(static_cast<T*>(p.y) + m * p.n + n) = pack2<T>(o0, o1);
+  } else {
+    qkv_epilogue_pair<T>(p, m, n, v0, v1);
+  }
+}
+
+template <typename T>
+int splitk_finish_typed(int epi, const float* partial, int splits, const LinearParams& p, cudaStream_t st) {
+  const int64_t pairs = epi == EPI_SWIGLU ? p.n : (p.n >> 1);
+  const unsigned blocks = static_cast<unsigned>((pairs * p.m + 255) / 256);
+  if (epi == EPI_PLAIN)
+    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_PLAIN>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
+  else if (epi == EPI_SWIGLU)
+    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_SWIGLU>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
+  else
+    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_QKV>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
+  LRI_LAUNCH_CHECK("splitk_finish_kernel");
+  return LRI_OK;
+}
+
 unsigned blocks_for(int64_t items, int threads) { return static_cast<unsigned>((items + threads - 1) / threads); }
 
 }  // namespace
@@ -176,6 +235,33 @@ int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int
   return dtype == LRI_BF16 ? launch_simt<__nv_bfloat16>(a, w, c, m, n, k, st)
                            : launch_simt<__half>(a, w, c, m, n, k, st);
 }
+
+int splitk_finish_launch(int dtype, int epi, const float* partial, int splits, const LinearParams& p,
+                         cudaStream_t st) {
+  return dtype == LRI_BF16 ? splitk_finish_typed<__nv_bfloat16>(epi, partial, splits, p, st)
+                           : splitk_finish_typed<__half>(epi, partial, splits, p, st);
+}
+
+// Split-K plan for a projection with `cols` weight rows at M token rows: number of slices that
+// the caller's workspace can hold (0: use another path).  Projections with enough 128-row tiles
+// to fill the GPU several times over (the LM head) are not split.
+static int splitk_plan(int64_t M, int64_t cols, int K, const void* x, const void* w, const void* workspace,
+                       size_t workspace_bytes) {
+  if (M <= streaming_rows() || M > kSplitKMaxRows || current_gemm_backend() == LRI_GEMM_SIMT) return 0;
+  if (!gemm_tcgen05_supports(M, static_cast<int>(cols), K) || !aligned16(x) || !aligned16(w)) return 0;
+  if (workspace == nullptr || !aligned16(workspace)) return 0;
+  const size_t per_slice = static_cast<size_t>(M) * static_cast<size_t>(cols) * sizeof(float);
+  const size_t fit = workspace_bytes / per_slice;
+  if (fit == 0) return 0;
+  const int want = gemm_tcgen05_choose_splits(static_cast<int>(cols), K);
+  return want < static_cast<int>(fit) ? want : static_cast<int>(fit);
+}
+static size_t splitk_bytes(int64_t M, int64_t cols) {
+  if (M <= streaming_rows() || M > kSplitKMaxRows) return 0;
+  if ((cols + 127) / 128 >= 2 * 148) return 0;
+  return static_cast<size_t>(kMaxSplitK) * static_cast<size_t>(M) * static_cast<size_t>(cols) * sizeof(float);
+}
+static size_t max_size(size_t a, size_t b) { return a > b ? a : b; }
 
 int swiglu_rows_launch(int dtype, const void* ug, void* h, int64_t m, int n, cudaStream_t st) {
   const int64_t items = m * (n >> 3);
@@ -243,8 +329,6 @@ static int check_common(const char* who, int dtype, const void* x, const void* w
 
 extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M, int N,
                           int K, void* workspace, size_t workspace_bytes, lri_stream_t stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   int rc = check_common("linear", dtype, x, w, M, K);
   if (rc != LRI_OK) return rc;
   LRI_REQUIRE(y != nullptr && N > 0, LRI_ERR_ARG, "linear: y is NULL or N=%d", N);
@@ -255,6 +339,16 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
     p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
     return streaming_launch(dtype, EPI_PLAIN, p, st, prefer_simt_gemv());
   }
+  if ((N + 127) / 128 < 2 * 148 && N % 2 == 0) {
+    const int splits = splitk_plan(M, N, K, x, w, workspace, workspace_bytes);
+    if (splits > 0) {
+      rc = gemm_tcgen05_splitk_launch(dtype, x, w, static_cast<float*>(workspace), M, N, K, splits, st);
+      if (rc != LRI_OK) return rc;
+      LinearParams p{};
+      p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
+      return splitk_finish_launch(dtype, EPI_PLAIN, static_cast<const float*>(workspace), splits, p, st);
+    }
+  }
   rc = gemm_launch(dtype, x, w, y, M, N, K, st);
   if (rc != LRI_OK || addend == nullptr) return rc;
   LRI_REQUIRE((M * N) % 8 == 0 && aligned16(y) && aligned16(addend), LRI_ERR_ALIGN,
@@ -262,8 +356,13 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
   return add_rows_launch(dtype, y, addend, M * N, st);
 }
 
-extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
+extern "C" size_t lri_linear_workspace_bytes(int64_t M, int N) { return M < 0 || N <= 0 ? 0 : splitk_bytes(M, N); }
+
+static size_t gateup_raw_bytes(int64_t M, int I) {
   return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
+}
+extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
+  return max_size(gateup_raw_bytes(M, I), splitk_bytes(M, 2 * static_cast<int64_t>(I)));
 }
 
 extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t M, int I, int K,
@@ -279,16 +378,27 @@ extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void*
     return streaming_launch(dtype, EPI_SWIGLU, p, st, prefer_simt_gemv());
   }
   LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, streaming_rows());
-  LRI_REQUIRE(workspace && workspace_bytes >= lri_gateup_workspace_bytes(M, I) && aligned16(workspace) && aligned16(h),
+  LRI_REQUIRE(workspace && workspace_bytes >= gateup_raw_bytes(M, I) && aligned16(workspace) && aligned16(h),
               LRI_ERR_WORKSPACE, "gateup_swiglu: workspace of %zu bytes (16-byte aligned) required",
               lri_gateup_workspace_bytes(M, I));
+  if (const int splits = splitk_plan(M, 2 * static_cast<int64_t>(I), K, x, w1, workspace, workspace_bytes)) {
+    rc = gemm_tcgen05_splitk_launch(dtype, x, w1, static_cast<float*>(workspace), M, 2 * I, K, splits, st);
+    if (rc != LRI_OK) return rc;
+    LinearParams p{};
+    p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
+    return splitk_finish_launch(dtype, EPI_SWIGLU, static_cast<const float*>(workspace), splits, p, st);
+  }
   rc = gemm_launch(dtype, x, w1, workspace, M, 2 * I, K, st);
   if (rc != LRI_OK) return rc;
   return swiglu_rows_launch(dtype, workspace, h, M, I, st);
 }
 
-extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
+static size_t qkv_raw_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
   return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
+}
+extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
+  return max_size(qkv_raw_bytes(M, n_head, n_kv, head_dim),
+                  splitk_bytes(M, static_cast<int64_t>(n_head + 2 * n_kv) * head_dim));
 }
 
 extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void* rope_table,
@@ -316,9 +426,14 @@ extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, 
   p.q_out = q_out, p.k_cache = k_cache, p.v_cache = v_cache;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.head_dim = head_dim, p.smax = smax, p.table_rows = table_rows, p.table_gathered = table_gathered;
   if (M <= streaming_rows()) return streaming_launch(dtype, EPI_QKV, p, st, prefer_simt_gemv());
-  LRI_REQUIRE(workspace && workspace_bytes >= lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
+  LRI_REQUIRE(workspace && workspace_bytes >= qkv_raw_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
               LRI_ERR_WORKSPACE, "qkv_rope_kvcache: workspace of %zu bytes (16-byte aligned) required",
               lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim));
+  if (const int splits = splitk_plan(M, p.n, K, x, wqkv, workspace, workspace_bytes)) {
+    rc = gemm_tcgen05_splitk_launch(dtype, x, wqkv, static_cast<float*>(workspace), M, p.n, K, splits, st);
+    if (rc != LRI_OK) return rc;
+    return splitk_finish_launch(dtype, EPI_QKV, static_cast<const float*>(workspace), splits, p, st);
+  }
   rc = gemm_launch(dtype, x, wqkv, workspace, M, p.n, K, st);
   if (rc != LRI_OK) return rc;
   return qkv_scatter_launch(dtype, workspace, p, st);

@@ -61,10 +61,18 @@ class Engine:
         self.part_a, self.part_m = buf(self.d), buf(self.d)
         self.q, self.y = buf(self.nh * self.hd), buf(self.nh * self.hd)
         self.h = buf(self.inter)
-        nq = self.ops.qkv_workspace_bytes(rows, self.nh, self.nkv, self.hd)
-        ng = self.ops.gateup_workspace_bytes(rows, self.inter)
-        self.ws_qkv = torch.empty(nq, dtype=torch.uint8, device=device) if nq else None
-        self.ws_ug = torch.empty(ng, dtype=torch.uint8, device=device) if ng else None
+
+        def workspace(size_fn, *shape):
+            # large enough for a prefill of all rows and for a decode step of up to 64 rows (whose
+            # split-K partial sums can take more room than a longer prefill's raw projection)
+            n = max(size_fn(rows, *shape), size_fn(min(rows, 64), *shape))
+            return torch.empty(n, dtype=torch.uint8, device=device) if n else None
+
+        self.ws_qkv = workspace(self.ops.qkv_workspace_bytes, self.nh, self.nkv, self.hd)
+        self.ws_ug = workspace(self.ops.gateup_workspace_bytes, self.inter)
+        # wo and w2 may run at the same time on two streams: one workspace each (w2's also serves the LM head)
+        self.ws_wo = workspace(self.ops.linear_workspace_bytes, self.d)
+        self.ws_w2 = workspace(self.ops.linear_workspace_bytes, self.d)
         nbytes = self.ops.attn_decode_scratch_bytes(max_batch, self.nh, self.nkv, self.hd, _MAX_SPLITS)
         self.scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
         # ladder decode runs the attention and MLP chains of a layer on two streams (LRI_LADDER_OVERLAP=0: one)
@@ -87,14 +95,14 @@ class Engine:
         if push:
             self.comm.linear_push(self.y, att.wo.weight, out, rows, push)
         else:
-            ops.linear(self.y, att.wo.weight, out, rows)
+            ops.linear(self.y, att.wo.weight, out, rows, workspace=self.ws_wo)
 
     def _mlp(self, w1, w2, rows, out, addend=None, normed=None, push=0):
         self.ops.gateup_swiglu(self.normed if normed is None else normed, w1, self.h, rows, self.ws_ug)
         if push:
             self.comm.linear_push(self.h, w2, out, rows, push, addend=addend)
         else:
-            self.ops.linear(self.h, w2, out, rows, addend=addend)
+            self.ops.linear(self.h, w2, out, rows, addend=addend, workspace=self.ws_w2)
 
     def _norm(self, weight, rows, add1=None, add2=None, scale=1.0, write_residual=True, normed=None, ch1=0, ch2=0):
         """residual += adds (in place), normed = RMSNorm(residual) * weight.  With ch1 / ch2 > 0 the

@@ -34,11 +34,16 @@ class CudaOps:
 
     # ---- linear family -----------------------------------------------------------------------
     @staticmethod
-    def linear(x, w, out, rows, addend=None):
+    def linear(x, w, out, rows, addend=None, workspace=None):
         _C.require_cuda(x, w, out)
         n, k = w.shape
+        ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
         _C.check(_C.lib.lri_linear(_C.dtype_code(x.dtype), x.data_ptr(), w.data_ptr(), _C.ptr(addend), out.data_ptr(),
-                                   rows, n, k, None, 0, _C.stream_handle()))
+                                   rows, n, k, ws_ptr, ws_bytes, _C.stream_handle()))
+
+    @staticmethod
+    def linear_workspace_bytes(rows, n):
+        return _C.lib.lri_linear_workspace_bytes(rows, n)
 
     @staticmethod
     def qkv_workspace_bytes(rows, n_head, n_kv, head_dim):

@@ -98,12 +98,16 @@ def main():
                  torch.zeros(ops.attn_decode_scratch_bytes(B, nh, nkv, hd, splits), dtype=torch.uint8, device=dev)),
         lambda o: ops.attention(o[0], o[1], o[2], pos, o[3], B, 1, nh, nkv, hd, o[4], splits))
     # F5: wo and w2
+    def lin_ws(n):
+        nbytes = ops.linear_workspace_bytes(B, n)
+        return torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+
     add("wo", d * nh * hd * 2 + B * nh * hd * 2 + B * d * 2,
-        lambda: (rnd(B, nh * hd, scale=1), rnd(d, nh * hd), torch.empty(B, d, dtype=dt, device=dev)),
-        lambda o: ops.linear(o[0], o[1], o[2], B))
+        lambda: (rnd(B, nh * hd, scale=1), rnd(d, nh * hd), torch.empty(B, d, dtype=dt, device=dev), lin_ws(d)),
+        lambda o: ops.linear(o[0], o[1], o[2], B, workspace=o[3]))
     add("w2", d * inter * 2 + B * inter * 2 + B * d * 2,
-        lambda: (rnd(B, inter, scale=1), rnd(d, inter), torch.empty(B, d, dtype=dt, device=dev)),
-        lambda o: ops.linear(o[0], o[1], o[2], B))
+        lambda: (rnd(B, inter, scale=1), rnd(d, inter), torch.empty(B, d, dtype=dt, device=dev), lin_ws(d)),
+        lambda o: ops.linear(o[0], o[1], o[2], B, workspace=o[3]))
     # F6: gate/up + SwiGLU
     ws_bytes = ops.gateup_workspace_bytes(B, inter)
     add("gateup_swiglu", 2 * inter * d * 2 + B * d * 2 + B * inter * 2,
@@ -112,8 +116,9 @@ def main():
         lambda o: ops.gateup_swiglu(o[0], o[1], o[2], B, o[3]))
     # F7: LM head
     add("lm_head", s["vocab"] * d * 2 + B * d * 2 + B * s["vocab"] * 2,
-        lambda: (rnd(B, d, scale=1), rnd(s["vocab"], d), torch.empty(B, s["vocab"], dtype=dt, device=dev)),
-        lambda o: ops.linear(o[0], o[1], o[2], B))
+        lambda: (rnd(B, d, scale=1), rnd(s["vocab"], d), torch.empty(B, s["vocab"], dtype=dt, device=dev),
+                 lin_ws(s["vocab"])),
+        lambda o: ops.linear(o[0], o[1], o[2], B, workspace=o[3]))
 
     peak, kind = peak_gbs()
     rows = []

@@ -30,11 +30,15 @@ class CpuOps:
             normed_out[:rows] = lo.rmsnorm(x, weight, eps)
 
     @staticmethod
-    def linear(x, w, out, rows, addend=None):
+    def linear(x, w, out, rows, addend=None, workspace=None):
         y = lo.linear(x[:rows], w)
         if addend is not None:
             y = y + addend[:rows]
         out.view(-1, w.shape[0])[:rows] = y
+
+    @staticmethod
+    def linear_workspace_bytes(rows, n):
+        return 0
 
     @staticmethod
     def qkv_workspace_bytes(rows, n_head, n_kv, head_dim):

@@ -128,7 +128,30 @@ def test_linear_gemm(backend, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m", [1, 3, 8, 12, 16, 24, 200])
+@pytest.mark.parametrize("m", [17, 24, 33, 64])
+@pytest.mark.parametrize("n,k", GEMM_NK + [(256, 8192), (1024, 7168)])
+@pytest.mark.parametrize("ws_scale", [1.0, 0.3, 0.0])
+def test_linear_splitk(dtype, m, n, k, ws_scale):
+    """17..64 rows with a workspace: the tcgen05 GEMM cuts K into slices (as many as the workspace
+    holds; none without one) and a second kernel sums them and adds the addend."""
+    c, ops = _C(), _ops()
+    g = torch.Generator().manual_seed(m * 11 + n + k)
+    x, w = _randn(g, m, k, dtype=dtype), _randn(g, n, k, scale=1 / math.sqrt(k), dtype=dtype)
+    add = _randn(g, m, n, dtype=dtype)
+    nbytes = int(ops.linear_workspace_bytes(m, n) * ws_scale) // 16 * 16
+    assert ops.linear_workspace_bytes(m, n) == 8 * m * n * 4
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda") if nbytes else None
+    y = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    ops.linear(x.cuda(), w.cuda(), y, m, workspace=ws)
+    torch.cuda.synchronize()
+    c.check(c.lib.lri_gemm_status())
+    _ulp_close(y, lo.linear(x, w), dtype)
+    ops.linear(x.cuda(), w.cuda(), y, m, addend=add.cuda(), workspace=ws)
+    _ulp_close(y, lo.linear(x, w) + add, dtype, ulps=6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 3, 8, 12, 16, 24, 40, 64, 200])
 @pytest.mark.parametrize("inter,k", [(512, 256), (1000, 1024), (14336 // 8, 4096)])
 def test_gateup_swiglu(dtype, m, inter, k):
     g = torch.Generator().manual_seed(m + inter + k)
@@ -142,7 +165,7 @@ def test_gateup_swiglu(dtype, m, inter, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("B,S", [(1, 1), (3, 1), (2, 3), (2, 8), (2, 12), (1, 200)])
+@pytest.mark.parametrize("B,S", [(1, 1), (3, 1), (2, 3), (2, 8), (2, 12), (4, 10), (3, 20), (1, 200)])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128)])
 @pytest.mark.parametrize("gathered", [False, True])
 def test_qkv_rope_kvcache(dtype, B, S, nh, nkv, hd, gathered):
