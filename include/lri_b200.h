@@ -81,11 +81,12 @@ int lri_embedding(int dtype, const void* table, const void* idx, int idx_is_i64,
  * x [M, K], w [N, K], y [M, N].  addend (may be NULL) is added after y's own rounding and the
  * sum rounded again (the parallel block's `w2(...) + y`, gpt_fast/utils.py:385).  M <= 8 runs
  * the weight-streaming kernels (SIMT for one row, mma.sync for 2..8); larger M the tcgen05 GEMM.
- * For 8 < M <= 64 a workspace of lri_linear_workspace_bytes(M, N) bytes (16-byte aligned) lets
- * the tcgen05 GEMM cut K into slices so that a narrow projection still occupies every SM (fp32
- * partial sums in the workspace, summed by a second kernel that also applies the addend); with
- * NULL / a smaller workspace fewer or no slices are used.  Two calls that may run at the same
- * time on different streams need different workspaces.  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
+ * For 8 < M <= 64 a workspace of lri_linear_workspace_bytes(M, N) bytes (16-byte aligned) selects
+ * the tcgen05 stream-K kernel: all SMs stream equal shares of the weight, fp32 partial tiles go
+ * to the workspace and the CTA that completes a tile sums them and applies the addend.  With
+ * NULL or a smaller workspace the plain GEMM runs.  Two calls that may run at the same time on
+ * different streams need different workspaces; at most 16 stream-K kernels (this entry point,
+ * lri_qkv_rope_kvcache, lri_gateup_swiglu) may be in flight at once.  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
  * 258, 384-385 and gpt_fast/gpt_ladder_TP.py:283. */
 size_t lri_linear_workspace_bytes(int64_t M, int N);
 int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M,

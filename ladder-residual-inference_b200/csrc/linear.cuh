@@ -93,16 +93,17 @@ bool prefer_simt_gemv();
 // C[m, n] = A[m, k] * W[n, k]^T, C in `dtype`, any m.  backend: lri_gemm_backend.
 int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);
 
-// Small-batch decode above the streaming kernels (up to kSplitKMaxRows token rows): the tcgen05
-// GEMM with the weights as the 128-row operand and K cut into slices, fp32 partials in a
-// workspace, then one kernel that sums the slices and runs the projection's epilogue.
+// Small-batch decode above the streaming kernels (up to kSplitKMaxRows token rows): a tcgen05
+// stream-K GEMM with the weights as the 128-row operand, fp32 partial tiles in a workspace and
+// the projection's epilogue applied by the CTA that completes a tile (gemm_streamk.cu).
+// lin.n counts outputs (SWIGLU: the weight has 2 * lin.n rows).
 constexpr int kMaxSplitK = 8;
 constexpr int kSplitKMaxRows = 64;
-int gemm_tcgen05_choose_splits(int n, int k);
-int gemm_tcgen05_splitk_launch(int dtype, const void* a, const void* w, float* partial, int64_t m, int n, int k,
-                               int splits, cudaStream_t st);
-// p.m rows, p.n outputs (SWIGLU: partial has 2 * p.n columns); partial = [splits, p.m, columns] fp32
-int splitk_finish_launch(int dtype, int epi, const float* partial, int splits, const LinearParams& p, cudaStream_t st);
+size_t gemm_streamk_workspace_bytes(int epi, int64_t m, int n);
+bool gemm_streamk_supports(int epi, const LinearParams& lin, const void* workspace, size_t workspace_bytes);
+int gemm_streamk_launch(int dtype, int epi, const LinearParams& lin, void* workspace, size_t workspace_bytes,
+                        cudaStream_t st);
+int gemm_streamk_status_read_and_clear(int* status_out);
 
 // elementwise epilogues used after the GEMM on the prefill path
 int swiglu_rows_launch(int dtype, const void* ug /*[m, 2n]*/, void* h /*[m, n]*/, int64_t m, int n, cudaStream_t st);

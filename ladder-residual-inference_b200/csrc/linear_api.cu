@@ -164,64 +164,6 @@ __global__ void __launch_bounds__(256) add_rows_kernel(T* __restrict__ y, const 
   reinterpret_cast<uint4*>(y)[i] = pack8<T>(a);
 }
 
-// Sum of the K slices of a split-K GEMM followed by the projection's epilogue; one thread per
-// token row and output pair (PLAIN / QKV: columns 2j, 2j+1; SWIGLU: columns j and n + j).
-template <typename T, int EPI>
-__global__ void __launch_bounds__(256) splitk_finish_kernel(const float* __restrict__ partial, int splits,
-                                                            const LinearParams p) {
-  const int64_t pairs = EPI == EPI_SWIGLU ? p.n : (p.n >> 1);
-  const int64_t cols = EPI == EPI_SWIGLU ? 2 * static_cast<int64_t>(p.n) : p.n;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  pdl_wait();
-  pdl_launch_dependents();
-  if (idx >= pairs * p.m) return;
-  const int64_t m = idx / pairs;
-  const int64_t j = idx - m * pairs;
-  float s0 = 0.f, s1 = 0.f;
-  const float* src = partial + m * cols;
-  const int64_t slice = static_cast<int64_t>(p.m) * cols;
-  if (EPI == EPI_SWIGLU) {
-    for (int z = 0; z < splits; ++z) {
-      s0 += src[z * slice + j];
-      s1 += src[z * slice + p.n + j];
-    }
-    static_cast<T*>(p.y)[m * p.n + j] = swiglu_rounded<T>(rnd<T>(s0), rnd<T>(s1));
-    return;
-  }
-  for (int z = 0; z < splits; ++z) {
-    const float2 v = *reinterpret_cast<const float2*>(src + z * slice + 2 * j);
-    s0 += v.x;
-    s1 += v.y;
-  }
-  const float v0 = rnd<T>(s0), v1 = rnd<T>(s1);
-  const int64_t n = 2 * j;
-  if (EPI == EPI_PLAIN) {
-    float o0 = v0, o1 = v1;
-    if (p.addend) {
-      const T* add = static_cast<const T*>(p.addend) + m * p.n + n;
-      o0 = rnd<T>(v0 + Num<T>::to_f(add[0]));
-      o1 = rnd<T>(v1 + Num<T>::to_f(add[1]));
-    }
-    *reinterpret_cast<uint32_t*>(static_cast<T*>(p.y) + m * p.n + n) = pack2<T>(o0, o1);
-  } else {
-    qkv_epilogue_pair<T>(p, m, n, v0, v1);
-  }
-}
-
-template <typename T>
-int splitk_finish_typed(int epi, const float* partial, int splits, const LinearParams& p, cudaStream_t st) {
-  const int64_t pairs = epi == EPI_SWIGLU ? p.n : (p.n >> 1);
-  const unsigned blocks = static_cast<unsigned>((pairs * p.m + 255) / 256);
-  if (epi == EPI_PLAIN)
-    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_PLAIN>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
-  else if (epi == EPI_SWIGLU)
-    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_SWIGLU>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
-  else
-    LRI_CUDA(launch_pdl(splitk_finish_kernel<T, EPI_QKV>, dim3(blocks), dim3(256), 0, st, partial, splits, p));
-  LRI_LAUNCH_CHECK("splitk_finish_kernel");
-  return LRI_OK;
-}
-
 unsigned blocks_for(int64_t items, int threads) { return static_cast<unsigned>((items + threads - 1) / threads); }
 
 }  // namespace
@@ -236,30 +178,12 @@ int gemm_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int
                            : launch_simt<__half>(a, w, c, m, n, k, st);
 }
 
-int splitk_finish_launch(int dtype, int epi, const float* partial, int splits, const LinearParams& p,
-                         cudaStream_t st) {
-  return dtype == LRI_BF16 ? splitk_finish_typed<__nv_bfloat16>(epi, partial, splits, p, st)
-                           : splitk_finish_typed<__half>(epi, partial, splits, p, st);
+// The stream-K path serves token rows above the streaming kernels and up to kSplitKMaxRows.
+static bool streamk_rows(int64_t M) {
+  return M > streaming_rows() && M <= kSplitKMaxRows && current_gemm_backend() != LRI_GEMM_SIMT;
 }
-
-// Split-K plan for a projection with `cols` weight rows at M token rows: number of slices that
-// the caller's workspace can hold (0: use another path).  Projections with enough 128-row tiles
-// to fill the GPU several times over (the LM head) are not split.
-static int splitk_plan(int64_t M, int64_t cols, int K, const void* x, const void* w, const void* workspace,
-                       size_t workspace_bytes) {
-  if (M <= streaming_rows() || M > kSplitKMaxRows || current_gemm_backend() == LRI_GEMM_SIMT) return 0;
-  if (!gemm_tcgen05_supports(M, static_cast<int>(cols), K) || !aligned16(x) || !aligned16(w)) return 0;
-  if (workspace == nullptr || !aligned16(workspace)) return 0;
-  const size_t per_slice = static_cast<size_t>(M) * static_cast<size_t>(cols) * sizeof(float);
-  const size_t fit = workspace_bytes / per_slice;
-  if (fit == 0) return 0;
-  const int want = gemm_tcgen05_choose_splits(static_cast<int>(cols), K);
-  return want < static_cast<int>(fit) ? want : static_cast<int>(fit);
-}
-static size_t splitk_bytes(int64_t M, int64_t cols) {
-  if (M <= streaming_rows() || M > kSplitKMaxRows) return 0;
-  if ((cols + 127) / 128 >= 2 * 148) return 0;
-  return static_cast<size_t>(kMaxSplitK) * static_cast<size_t>(M) * static_cast<size_t>(cols) * sizeof(float);
+static size_t streamk_bytes(int epi, int64_t M, int64_t n) {
+  return (M > streaming_rows() && M <= kSplitKMaxRows && n < (1ll << 31)) ? gemm_streamk_workspace_bytes(epi, M, static_cast<int>(n)) : 0;
 }
 static size_t max_size(size_t a, size_t b) { return a > b ? a : b; }
 
@@ -311,10 +235,13 @@ extern "C" int lri_set_gemm_backend(int backend) {
   return LRI_OK;
 }
 extern "C" int lri_gemm_status(void) {
-  int v = 0;
+  int v = 0, v2 = 0;
   int rc = gemm_tcgen05_status_read_and_clear(&v);
   if (rc != LRI_OK) return rc;
-  if (v != 0) return fail(LRI_ERR_TIMEOUT, "tcgen05 GEMM: a bounded mbarrier wait gave up (site %d)", v);
+  rc = gemm_streamk_status_read_and_clear(&v2);
+  if (rc != LRI_OK) return rc;
+  if (v != 0 || v2 != 0)
+    return fail(LRI_ERR_TIMEOUT, "tcgen05 GEMM: a bounded mbarrier wait gave up (site %d)", v != 0 ? v : v2);
   return LRI_OK;
 }
 
@@ -339,15 +266,11 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
     p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
     return streaming_launch(dtype, EPI_PLAIN, p, st, prefer_simt_gemv());
   }
-  if ((N + 127) / 128 < 2 * 148 && N % 2 == 0) {
-    const int splits = splitk_plan(M, N, K, x, w, workspace, workspace_bytes);
-    if (splits > 0) {
-      rc = gemm_tcgen05_splitk_launch(dtype, x, w, static_cast<float*>(workspace), M, N, K, splits, st);
-      if (rc != LRI_OK) return rc;
-      LinearParams p{};
-      p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
-      return splitk_finish_launch(dtype, EPI_PLAIN, static_cast<const float*>(workspace), splits, p, st);
-    }
+  if (streamk_rows(M)) {
+    LinearParams p{};
+    p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
+    if (gemm_streamk_supports(EPI_PLAIN, p, workspace, workspace_bytes))
+      return gemm_streamk_launch(dtype, EPI_PLAIN, p, workspace, workspace_bytes, st);
   }
   rc = gemm_launch(dtype, x, w, y, M, N, K, st);
   if (rc != LRI_OK || addend == nullptr) return rc;
@@ -356,13 +279,13 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
   return add_rows_launch(dtype, y, addend, M * N, st);
 }
 
-extern "C" size_t lri_linear_workspace_bytes(int64_t M, int N) { return M < 0 || N <= 0 ? 0 : splitk_bytes(M, N); }
+extern "C" size_t lri_linear_workspace_bytes(int64_t M, int N) { return M < 0 || N <= 0 ? 0 : streamk_bytes(EPI_PLAIN, M, N); }
 
 static size_t gateup_raw_bytes(int64_t M, int I) {
   return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
 }
 extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
-  return max_size(gateup_raw_bytes(M, I), splitk_bytes(M, 2 * static_cast<int64_t>(I)));
+  return max_size(gateup_raw_bytes(M, I), streamk_bytes(EPI_SWIGLU, M, I));
 }
 
 extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t M, int I, int K,
@@ -381,12 +304,11 @@ extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void*
   LRI_REQUIRE(workspace && workspace_bytes >= gateup_raw_bytes(M, I) && aligned16(workspace) && aligned16(h),
               LRI_ERR_WORKSPACE, "gateup_swiglu: workspace of %zu bytes (16-byte aligned) required",
               lri_gateup_workspace_bytes(M, I));
-  if (const int splits = splitk_plan(M, 2 * static_cast<int64_t>(I), K, x, w1, workspace, workspace_bytes)) {
-    rc = gemm_tcgen05_splitk_launch(dtype, x, w1, static_cast<float*>(workspace), M, 2 * I, K, splits, st);
-    if (rc != LRI_OK) return rc;
+  if (streamk_rows(M)) {
     LinearParams p{};
     p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
-    return splitk_finish_launch(dtype, EPI_SWIGLU, static_cast<const float*>(workspace), splits, p, st);
+    if (gemm_streamk_supports(EPI_SWIGLU, p, workspace, workspace_bytes))
+      return gemm_streamk_launch(dtype, EPI_SWIGLU, p, workspace, workspace_bytes, st);
   }
   rc = gemm_launch(dtype, x, w1, workspace, M, 2 * I, K, st);
   if (rc != LRI_OK) return rc;
@@ -398,7 +320,7 @@ static size_t qkv_raw_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
 }
 extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
   return max_size(qkv_raw_bytes(M, n_head, n_kv, head_dim),
-                  splitk_bytes(M, static_cast<int64_t>(n_head + 2 * n_kv) * head_dim));
+                  streamk_bytes(EPI_QKV, M, static_cast<int64_t>(n_head + 2 * n_kv) * head_dim));
 }
 
 extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, const void* rope_table,
@@ -429,11 +351,8 @@ extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, 
   LRI_REQUIRE(workspace && workspace_bytes >= qkv_raw_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
               LRI_ERR_WORKSPACE, "qkv_rope_kvcache: workspace of %zu bytes (16-byte aligned) required",
               lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim));
-  if (const int splits = splitk_plan(M, p.n, K, x, wqkv, workspace, workspace_bytes)) {
-    rc = gemm_tcgen05_splitk_launch(dtype, x, wqkv, static_cast<float*>(workspace), M, p.n, K, splits, st);
-    if (rc != LRI_OK) return rc;
-    return splitk_finish_launch(dtype, EPI_QKV, static_cast<const float*>(workspace), splits, p, st);
-  }
+  if (streamk_rows(M) && gemm_streamk_supports(EPI_QKV, p, workspace, workspace_bytes))
+    return gemm_streamk_launch(dtype, EPI_QKV, p, workspace, workspace_bytes, st);
   rc = gemm_launch(dtype, x, wqkv, workspace, M, p.n, K, st);
   if (rc != LRI_OK) return rc;
   return qkv_scatter_launch(dtype, workspace, p, st);
