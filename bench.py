@@ -54,10 +54,31 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
+                    help="prefill: time the prompt pass alone (tensor-core bound; an extra measurement, not the default metric)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly (for kernel profiling)")
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers in the CPU sample")
     return ap.parse_args()
+
+
+def measured_tensor_peak():
+    """Sustained dense bf16 TFLOP/s of this pool's B200s (the prompt pass is a long tensor-core job)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1400.0, "fallback"
+
+
+def prefill_flops(a, t, batch, seq):
+    """Algorithmic FLOPs of one prompt pass per rank: projections, causal attention, LM head on every position."""
+    d, L, V = a["dim"], a["n_layer"], a["vocab_size"]
+    nh, nkv, hd, inter = a["n_head"], a["n_local_heads"], a["head_dim"], a["intermediate_size"]
+    proj = 2 * batch * seq * L * ((nh + 2 * nkv) * hd * d + nh * hd * d + 3 * inter * d) // t
+    attn = 4 * batch * seq * seq * (nh // t) * hd * L // 2
+    head = 2 * batch * seq * V * d
+    return proj + attn + head
 
 
 def measured_hbm_peak():
@@ -276,6 +297,9 @@ def run_ours(args):
     del logits
     torch.cuda.synchronize()
 
+    if args.mode == "prefill":
+        return run_prefill(args, a, model, x, comm, rank, world, dev)
+
     tok = first.clone()
     pos = torch.tensor([T], dtype=torch.int32, device=dev)
     nxt = torch.empty_like(tok)
@@ -392,6 +416,58 @@ def run_ours(args):
             "value": tps, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{args.cpu_layers} of {a['n_layer']} layers + final norm + LM head of one decode step at context "
                       f"{T}, fp32, batch {B}, 3 timed steps, layer time scaled to full depth"}
+    print(json.dumps(line), flush=True)
+
+
+def run_prefill(args, a, model, x, comm, rank, world, dev):
+    """Prompt pass alone: K timed calls of model(prompt, arange(T)) after W warm-up calls."""
+    import torch
+    import torch.distributed as dist
+    from gpt_fast import _C
+    B, T, K, W = args.batch, args.prompt, args.steps, args.warmup
+    positions = torch.arange(T, device=dev)
+    c0 = _C.lib.lri_launch_count()
+    with torch.no_grad():
+        for _ in range(W):
+            model(x, positions)
+        launches = (_C.lib.lri_launch_count() - c0) // max(W, 1)
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device())
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.25)
+        t0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            model(x, positions)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = ms.item()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    comm.status()
+    _C.check(_C.lib.lri_gemm_status())
+    if rank != 0:
+        return
+    flops = prefill_flops(a, world, B, T)
+    peak, kind = measured_tensor_peak()
+    achieved = flops / (ms / K / 1e3) / 1e12
+    line = {
+        "metric": "prefill tokens/s", "value": B * T * K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": f"gpt_{args.family}:{args.preset} prompt pass, batch {B}, {T} random ids per sequence, "
+                               f"logits for every position, TP={world}", "comm": comm.name,
+                   "l2": "operands of every GEMM exceed the 126 MB L2"},
+        "clocks": clocks, "gpu_launches": int(launches * K), "launches_per_step": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_kind": f"{kind} sustained cuBLAS bf16", "flops_per_rank_per_step": flops, "traffic": None},
+    }
     print(json.dumps(line), flush=True)
 
 

@@ -37,11 +37,21 @@ struct WorkItem {
 };
 struct GemmGrid {
   int tiles_p, tiles_q;
+  int group;  // P tiles per panel
 };
+// Order of the output tiles.  The P tiles are taken in panels of `group`; inside a panel the
+// Q tile is the slow index.  The CTAs that run at the same time then share one panel of P
+// (a few MB, stays in L2) and a handful of Q tiles, each of which all of them use at once, so
+// that both operands come from DRAM about once per panel instead of once per P tile.
 __device__ __forceinline__ WorkItem work_item(int item, const GemmGrid& g) {
   WorkItem w;
-  w.tile_p = item / g.tiles_q;  // neighbouring CTAs share the 128-row operand tile and stream different Q tiles
-  w.tile_q = item - w.tile_p * g.tiles_q;
+  const int panel_items = g.group * g.tiles_q;
+  const int panel = item / panel_items;
+  const int r = item - panel * panel_items;
+  const int p0 = panel * g.group;
+  const int gm = min(g.group, g.tiles_p - p0);
+  w.tile_q = r / gm;
+  w.tile_p = p0 + (r - w.tile_q * gm);
   return w;
 }
 
@@ -297,7 +307,16 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
   const int64_t tiles_p = (p_rows + kBM - 1) / kBM, tiles_q = (q_rows + BN - 1) / BN;
   const int64_t items = tiles_p * tiles_q;
   if (items >= (1ll << 31)) return fail(LRI_ERR_UNSUPPORTED, "gemm: %lld output tiles", (long long)items);
-  GemmGrid grid{static_cast<int>(tiles_p), static_cast<int>(tiles_q)};
+  // panel of P tiles: about 16 MB of the P operand, between 4 and 16 tiles (LRI_GEMM_GROUP overrides)
+  static const int forced_group = [] {
+    const char* e = getenv("LRI_GEMM_GROUP");
+    return e ? atoi(e) : 0;
+  }();
+  int64_t group = (16ll << 20) / (static_cast<int64_t>(kBM) * k * 2);
+  group = group < 4 ? 4 : (group > 16 ? 16 : group);
+  if (forced_group > 0) group = forced_group;
+  group = group > tiles_p ? tiles_p : group;
+  GemmGrid grid{static_cast<int>(tiles_p), static_cast<int>(tiles_q), static_cast<int>(group)};
   GemmShape shape{static_cast<int>(m), n, k};
   const int ctas = static_cast<int>(items < sm_count() ? items : sm_count());
   LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tp, tq,
