@@ -63,10 +63,17 @@ __device__ __forceinline__ WorkItem work_item(int item, const GemmGrid& g) {
 // ring keeps running across items (the producer is already fetching the next item's operands
 // while the last MMAs of the current one execute) and the accumulator is double-buffered in
 // TMEM, so the epilogue of item i overlaps the main loop of item i + 1.
-template <typename T, int BN, bool SWAP>
+//
+// EPI (SWAP == false only) fuses the projection's epilogue into the store of the tile:
+//   EPI_SWIGLU  the Q tile is BN/2 up rows followed by the BN/2 matching gate rows of w1, so that a
+//               thread finds up_j and gate_j of its token in the same accumulator row; it stores
+//               silu(gate) * up to h [m, I] (lin.y, lin.n = I)
+//   EPI_QKV     a thread rotates the 16 adjacent pairs of each 32-column chunk of its token with the
+//               table row of the token's position and stores them to q_out / k-cache / v-cache
+template <typename T, int BN, bool SWAP, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
-                    T* __restrict__ c, GemmShape shape, GemmGrid grid, int stages) {
+                    T* __restrict__ c, GemmShape shape, GemmGrid grid, int stages, const LinearParams lin) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t kTileP = kBM * kBK * 2;
   constexpr uint32_t kTileQ = BN * kBK * 2;
@@ -132,7 +139,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
           const uint32_t dst = base + s * kStageBytes;
           const int kx = kt * kBK;
           tma_load_2d(dst, &tmap_p, full0 + 8 * s, kx, w.tile_p * kBM);
-          tma_load_2d(dst + kTileP, &tmap_q, full0 + 8 * s, kx, w.tile_q * BN);
+          if (EPI == EPI_SWIGLU) {
+            tma_load_2d(dst + kTileP, &tmap_q, full0 + 8 * s, kx, w.tile_q * (BN / 2));
+            tma_load_2d(dst + kTileP + kTileQ / 2, &tmap_q, full0 + 8 * s, kx, lin.n + w.tile_q * (BN / 2));
+          } else {
+            tma_load_2d(dst + kTileP, &tmap_q, full0 + 8 * s, kx, w.tile_q * BN);
+          }
         }
       }
     }
@@ -183,10 +195,88 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
       const uint32_t use = static_cast<uint32_t>(it) >> 1;
       if (!mbar_wait(acc_full0 + 8 * a, use & 1u, &abort_flag, 3, &g_gemm_status)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kAccCols;
+      if (!SWAP && EPI == EPI_SWIGLU) {
+        const int64_t row = static_cast<int64_t>(w.tile_p) * kBM + i;
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 2; cc += 32) {
+          uint32_t up[32], gate[32];
+          tmem_ld32(tacc + cc, up);
+          tmem_ld32(tacc + BN / 2 + cc, gate);
+          const int64_t j0 = static_cast<int64_t>(w.tile_q) * (BN / 2) + cc;
+          if (row >= shape.m || j0 >= lin.n) continue;
+          T* dst = static_cast<T*>(lin.y) + row * lin.n + j0;
+          __align__(16) T out[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            out[e] = swiglu_rounded<T>(rnd<T>(__uint_as_float(up[e])), rnd<T>(__uint_as_float(gate[e])));
+          if (j0 + 32 <= lin.n && (lin.n & 7) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(out)[v];
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (j0 + e < lin.n) dst[e] = out[e];
+          }
+        }
+      } else if (!SWAP && EPI == EPI_QKV) {
+        const int64_t row = static_cast<int64_t>(w.tile_p) * kBM + i;
+        const int hd = lin.head_dim;
+        const int64_t nq = static_cast<int64_t>(lin.n_head) * hd, nk = static_cast<int64_t>(lin.n_kv) * hd;
+        const int64_t b = row / lin.S, sq = row - b * lin.S;
+        int64_t pos = 0, trow = 0;
+        bool live = row < shape.m;
+        if (live) {
+          pos = load_pos(lin.input_pos, lin.pos_is_i64, sq);
+          trow = lin.table_gathered ? sq : pos;
+          live = pos >= 0 && pos < lin.smax && trow < lin.table_rows;
+        }
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+          uint32_t r[32];
+          tmem_ld32(tacc + cc, r);
+          const int64_t n = static_cast<int64_t>(w.tile_q) * BN + cc;  // a 32-column chunk never straddles a head
+          if (!live || n >= shape.n) continue;
+          float f[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) f[e] = rnd<T>(__uint_as_float(r[e]));
+          T* dst;
+          if (n < nq + nk) {
+            const int64_t nn = n < nq ? n : n - nq;
+            const int e0 = static_cast<int>(nn % hd);
+            const uint4* cs = reinterpret_cast<const uint4*>(static_cast<const T*>(lin.rope_table) +
+                                                             (trow * (hd >> 1) + (e0 >> 1)) * 2);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float t[8];
+              unpack8<T>(cs[v], t);  // (cos, sin) of 4 pairs
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float o0, o1;
+                rope_pair(f[v * 8 + 2 * q], f[v * 8 + 2 * q + 1], t[2 * q], t[2 * q + 1], o0, o1);
+                f[v * 8 + 2 * q] = o0;
+                f[v * 8 + 2 * q + 1] = o1;
+              }
+            }
+            dst = n < nq ? static_cast<T*>(lin.q_out) + row * nq + n
+                         : static_cast<T*>(lin.k_cache) + ((b * lin.n_kv + nn / hd) * lin.smax + pos) * hd + e0;
+          } else {
+            const int64_t nn = n - nq - nk;
+            dst = static_cast<T*>(lin.v_cache) + ((b * lin.n_kv + nn / hd) * lin.smax + pos) * hd + nn % hd;
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float g8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g8[e] = f[v * 8 + e];
+            reinterpret_cast<uint4*>(dst)[v] = pack8<T>(g8);
+          }
+        }
+      } else
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kAccCols + cc;
+        const uint32_t taddr = tacc + cc;
         tmem_ld32(taddr, r);  // BN == 16: only the first 16 columns are valid (32 are allocated)
         constexpr int kValid = BN < 32 ? BN : 32;
         if (!SWAP) {
@@ -283,8 +373,9 @@ int sm_count() {
 
 namespace {
 
-template <typename T, int BN, bool SWAP>
-int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st) {
+template <typename T, int BN, bool SWAP, int EPI = EPI_PLAIN>
+int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st,
+                const LinearParams* lin = nullptr) {
   CUtensorMap tp, tq;
   const void* p_ptr = SWAP ? w : a;
   const void* q_ptr = SWAP ? a : w;
@@ -292,19 +383,21 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
   const int64_t q_rows = SWAP ? m : n;
   int rc = make_tmap(&tp, dtype, p_ptr, p_rows, k, kBM);
   if (rc != LRI_OK) return rc;
-  rc = make_tmap(&tq, dtype, q_ptr, q_rows, k, BN);
+  rc = make_tmap(&tq, dtype, q_ptr, q_rows, k, EPI == EPI_SWIGLU ? BN / 2 : BN);
   if (rc != LRI_OK) return rc;
   constexpr int kStageBytes = (kBM + BN) * kBK * 2;
   int stages = kSmemBudget / kStageBytes;
   stages = stages > 8 ? 8 : stages;
   const int smem = stages * kStageBytes + 1024;
-  auto kern = gemm_tcgen05_kernel<T, BN, SWAP>;
+  auto kern = gemm_tcgen05_kernel<T, BN, SWAP, EPI>;
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
     attr_set = true;
   }
-  const int64_t tiles_p = (p_rows + kBM - 1) / kBM, tiles_q = (q_rows + BN - 1) / BN;
+  const int64_t tiles_p = (p_rows + kBM - 1) / kBM;
+  // SWIGLU: a Q tile is BN/2 outputs (their up rows and their gate rows)
+  const int64_t tiles_q = EPI == EPI_SWIGLU ? (lin->n + BN / 2 - 1) / (BN / 2) : (q_rows + BN - 1) / BN;
   const int64_t items = tiles_p * tiles_q;
   if (items >= (1ll << 31)) return fail(LRI_ERR_UNSUPPORTED, "gemm: %lld output tiles", (long long)items);
   // panel of P tiles: about 16 MB of the P operand, between 4 and 16 tiles (LRI_GEMM_GROUP overrides)
@@ -320,7 +413,7 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
   GemmShape shape{static_cast<int>(m), n, k};
   const int ctas = static_cast<int>(items < sm_count() ? items : sm_count());
   LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tp, tq,
-                      static_cast<T*>(c), shape, grid, stages));
+                      static_cast<T*>(c), shape, grid, stages, lin ? *lin : LinearParams{}));
   LRI_LAUNCH_CHECK("gemm_tcgen05_kernel");
   return LRI_OK;
 }
@@ -331,7 +424,7 @@ int launch_typed(int dtype, const void* a, const void* w, void* c, int64_t m, in
   if (m <= 32) return launch_tile<T, 32, true>(dtype, a, w, c, m, n, k, st);
   if (m <= 64) return launch_tile<T, 64, true>(dtype, a, w, c, m, n, k, st);
   // prefill: pick the N tile that leaves fewer idle SMs in the last wave
-  int sms = 148;
+  const int sms = sm_count();
   const int64_t mt = (m + kBM - 1) / kBM;
   const int64_t t256 = mt * ((n + 255) / 256), t128 = mt * ((n + 127) / 128);
   // measured: a 128x256 tile takes about 1.1x the time of a 128x128 tile (1141 vs 623 TFLOP/s)
@@ -340,7 +433,40 @@ int launch_typed(int dtype, const void* a, const void* w, void* c, int64_t m, in
   return launch_tile<T, 128, false>(dtype, a, w, c, m, n, k, st);
 }
 
+// prefill with the epilogue fused: the same tile choice, counted in output tiles
+template <typename T, int EPI>
+int launch_fused(int dtype, const LinearParams& p, int64_t m, cudaStream_t st) {
+  const int n_rows = EPI == EPI_SWIGLU ? 2 * p.n : p.n;       // rows of the weight
+  const int64_t mt = (m + kBM - 1) / kBM;
+  const int w256 = EPI == EPI_SWIGLU ? 128 : 256, w128 = EPI == EPI_SWIGLU ? 64 : 128;  // outputs per Q tile
+  const int64_t t256 = mt * ((p.n + w256 - 1) / w256), t128 = mt * ((p.n + w128 - 1) / w128);
+  const int sms = sm_count();
+  const int64_t cost256 = ((t256 + sms - 1) / sms) * 110, cost128 = ((t128 + sms - 1) / sms) * 100;
+  if (cost256 <= cost128) return launch_tile<T, 256, false, EPI>(dtype, p.x, p.w, nullptr, m, n_rows, p.k, st, &p);
+  return launch_tile<T, 128, false, EPI>(dtype, p.x, p.w, nullptr, m, n_rows, p.k, st, &p);
+}
+
 }  // namespace
+
+bool gemm_tcgen05_supports(int64_t m, int n, int k);
+
+// Prefill-sized projections (more than 64 token rows) with the SwiGLU or the RoPE + KV-cache
+// epilogue applied from the accumulator: p.m token rows, p.n outputs (SWIGLU: I), all epilogue fields set.
+bool gemm_tcgen05_fused_supports(int epi, const LinearParams& p, int64_t m) {
+  if (m <= 64 || !gemm_tcgen05_supports(m, epi == EPI_SWIGLU ? 2 * p.n : p.n, p.k)) return false;
+  if (epi == EPI_SWIGLU) return aligned16(p.y);
+  if (epi == EPI_QKV) return p.head_dim % 32 == 0 && aligned16(p.rope_table);
+  return false;
+}
+
+int gemm_tcgen05_fused_launch(int dtype, int epi, const LinearParams& p, int64_t m, cudaStream_t st) {
+  if (!gemm_tcgen05_fused_supports(epi, p, m)) return fail(LRI_ERR_ARG, "gemm: fused epilogue not available for this shape");
+  if (epi == EPI_SWIGLU)
+    return dtype == LRI_BF16 ? launch_fused<__nv_bfloat16, EPI_SWIGLU>(dtype, p, m, st)
+                             : launch_fused<__half, EPI_SWIGLU>(dtype, p, m, st);
+  return dtype == LRI_BF16 ? launch_fused<__nv_bfloat16, EPI_QKV>(dtype, p, m, st)
+                           : launch_fused<__half, EPI_QKV>(dtype, p, m, st);
+}
 
 bool gemm_tcgen05_supports(int64_t m, int n, int k) {
   return m >= 1 && m < (1ll << 31) && n >= 8 && n % 8 == 0 && k >= 8 && k % 8 == 0;

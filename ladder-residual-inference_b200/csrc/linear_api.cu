@@ -15,6 +15,8 @@ namespace lri {
 bool gemm_tcgen05_supports(int64_t m, int n, int k);
 int gemm_tcgen05_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);
 int gemm_tcgen05_status_read_and_clear(int* status_out);
+bool gemm_tcgen05_fused_supports(int epi, const LinearParams& p, int64_t m);
+int gemm_tcgen05_fused_launch(int dtype, int epi, const LinearParams& p, int64_t m, cudaStream_t st);
 
 // ---- error text, launch counter, back-end switch ----------------------------------------------
 namespace {
@@ -55,6 +57,15 @@ int streaming_rows() {
     return v < 1 ? 1 : (v > kGemvMmaMaxRows ? kGemvMmaMaxRows : v);
   }();
   return rows;
+}
+// LRI_FUSED_PREFILL=0 keeps the prefill projections on the plain GEMM followed by an elementwise
+// kernel (debugging aid; also what runs for shapes the fused epilogues do not take).
+bool fused_prefill_epilogues() {
+  static const bool on = [] {
+    const char* e = getenv("LRI_FUSED_PREFILL");
+    return !(e && strcmp(e, "0") == 0);
+  }();
+  return on;
 }
 bool prefer_simt_gemv() {
   static const bool simt = [] {
@@ -272,6 +283,11 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
     if (gemm_streamk_supports(EPI_PLAIN, p, workspace, workspace_bytes))
       return gemm_streamk_launch(dtype, EPI_PLAIN, p, workspace, workspace_bytes, st);
   }
+  if (M <= kGemvMmaMaxRows) {  // no usable workspace: the streaming kernel takes up to 16 rows
+    LinearParams p{};
+    p.x = x, p.w = w, p.y = y, p.addend = addend, p.m = static_cast<int>(M), p.n = N, p.k = K;
+    return streaming_launch(dtype, EPI_PLAIN, p, st, prefer_simt_gemv());
+  }
   rc = gemm_launch(dtype, x, w, y, M, N, K, st);
   if (rc != LRI_OK || addend == nullptr) return rc;
   LRI_REQUIRE((M * N) % 8 == 0 && aligned16(y) && aligned16(addend), LRI_ERR_ALIGN,
@@ -282,7 +298,7 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
 extern "C" size_t lri_linear_workspace_bytes(int64_t M, int N) { return M < 0 || N <= 0 ? 0 : streamk_bytes(EPI_PLAIN, M, N); }
 
 static size_t gateup_raw_bytes(int64_t M, int I) {
-  return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
+  return M <= kGemvMmaMaxRows ? 0 : static_cast<size_t>(M) * 2 * static_cast<size_t>(I) * 2;
 }
 extern "C" size_t lri_gateup_workspace_bytes(int64_t M, int I) {
   return max_size(gateup_raw_bytes(M, I), streamk_bytes(EPI_SWIGLU, M, I));
@@ -295,28 +311,28 @@ extern "C" int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void*
   LRI_REQUIRE(h != nullptr && I > 0, LRI_ERR_ARG, "gateup_swiglu: h is NULL or I=%d", I);
   if (M == 0) return LRI_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M <= streaming_rows()) {
-    LinearParams p{};
-    p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
-    return streaming_launch(dtype, EPI_SWIGLU, p, st, prefer_simt_gemv());
-  }
-  LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, streaming_rows());
+  LinearParams p{};
+  p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
+  if (M <= streaming_rows()) return streaming_launch(dtype, EPI_SWIGLU, p, st, prefer_simt_gemv());
+  if (streamk_rows(M) && gemm_streamk_supports(EPI_SWIGLU, p, workspace, workspace_bytes))
+    return gemm_streamk_launch(dtype, EPI_SWIGLU, p, workspace, workspace_bytes, st);
+  // no usable workspace: the streaming kernel takes up to 16 rows
+  if (M <= kGemvMmaMaxRows) return streaming_launch(dtype, EPI_SWIGLU, p, st, prefer_simt_gemv());
+  LRI_REQUIRE(I % 8 == 0, LRI_ERR_UNSUPPORTED, "gateup_swiglu: I=%d must be a multiple of 8 for M > %d", I, kGemvMmaMaxRows);
+  // prefill: SwiGLU applied from the accumulator, no workspace needed
+  if (M > kSplitKMaxRows && current_gemm_backend() != LRI_GEMM_SIMT && fused_prefill_epilogues() &&
+      gemm_tcgen05_fused_supports(EPI_SWIGLU, p, M))
+    return gemm_tcgen05_fused_launch(dtype, EPI_SWIGLU, p, M, st);
   LRI_REQUIRE(workspace && workspace_bytes >= gateup_raw_bytes(M, I) && aligned16(workspace) && aligned16(h),
               LRI_ERR_WORKSPACE, "gateup_swiglu: workspace of %zu bytes (16-byte aligned) required",
               lri_gateup_workspace_bytes(M, I));
-  if (streamk_rows(M)) {
-    LinearParams p{};
-    p.x = x, p.w = w1, p.y = h, p.m = static_cast<int>(M), p.n = I, p.k = K;
-    if (gemm_streamk_supports(EPI_SWIGLU, p, workspace, workspace_bytes))
-      return gemm_streamk_launch(dtype, EPI_SWIGLU, p, workspace, workspace_bytes, st);
-  }
   rc = gemm_launch(dtype, x, w1, workspace, M, 2 * I, K, st);
   if (rc != LRI_OK) return rc;
   return swiglu_rows_launch(dtype, workspace, h, M, I, st);
 }
 
 static size_t qkv_raw_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
-  return M <= streaming_rows() ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
+  return M <= kGemvMmaMaxRows ? 0 : static_cast<size_t>(M) * static_cast<size_t>(n_head + 2 * n_kv) * head_dim * 2;
 }
 extern "C" size_t lri_qkv_workspace_bytes(int64_t M, int n_head, int n_kv, int head_dim) {
   return max_size(qkv_raw_bytes(M, n_head, n_kv, head_dim),
@@ -348,11 +364,17 @@ extern "C" int lri_qkv_rope_kvcache(int dtype, const void* x, const void* wqkv, 
   p.q_out = q_out, p.k_cache = k_cache, p.v_cache = v_cache;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.head_dim = head_dim, p.smax = smax, p.table_rows = table_rows, p.table_gathered = table_gathered;
   if (M <= streaming_rows()) return streaming_launch(dtype, EPI_QKV, p, st, prefer_simt_gemv());
+  if (streamk_rows(M) && gemm_streamk_supports(EPI_QKV, p, workspace, workspace_bytes))
+    return gemm_streamk_launch(dtype, EPI_QKV, p, workspace, workspace_bytes, st);
+  // no usable workspace: the streaming kernel takes up to 16 rows
+  if (M <= kGemvMmaMaxRows) return streaming_launch(dtype, EPI_QKV, p, st, prefer_simt_gemv());
+  // prefill: RoPE + cache write from the accumulator
+  if (M > kSplitKMaxRows && current_gemm_backend() != LRI_GEMM_SIMT && fused_prefill_epilogues() &&
+      gemm_tcgen05_fused_supports(EPI_QKV, p, M))
+    return gemm_tcgen05_fused_launch(dtype, EPI_QKV, p, M, st);
   LRI_REQUIRE(workspace && workspace_bytes >= qkv_raw_bytes(M, n_head, n_kv, head_dim) && aligned16(workspace),
               LRI_ERR_WORKSPACE, "qkv_rope_kvcache: workspace of %zu bytes (16-byte aligned) required",
               lri_qkv_workspace_bytes(M, n_head, n_kv, head_dim));
-  if (streamk_rows(M) && gemm_streamk_supports(EPI_QKV, p, workspace, workspace_bytes))
-    return gemm_streamk_launch(dtype, EPI_QKV, p, workspace, workspace_bytes, st);
   rc = gemm_launch(dtype, x, wqkv, workspace, M, p.n, K, st);
   if (rc != LRI_OK) return rc;
   return qkv_scatter_launch(dtype, workspace, p, st);
