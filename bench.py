@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
                     help="prefill: time the prompt pass alone (tensor-core bound; an extra measurement, not the default metric)")
+    ap.add_argument("--head", default="replicated", choices=["replicated", "vocab-parallel"],
+                    help="vocab-parallel: greedy choice through model.decode_greedy (output rows split over the ranks); "
+                         "replicated (default) is the reference's scheme")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly (for kernel profiling)")
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers in the CPU sample")
@@ -101,12 +104,13 @@ def shape_of(preset, family="ladder"):
     return a
 
 
-def step_bytes(a, t, batch, ctx):
+def step_bytes(a, t, batch, ctx, head_split=False):
     """Algorithmic HBM bytes of one decode step on one rank: every weight shard, norm weight and
-    the replicated LM head once, the valid part of the KV cache once, the new K/V once."""
+    the LM head once (all of it, or this rank's 1/t of the rows with the vocabulary-parallel greedy head),
+    the valid part of the KV cache once, the new K/V once."""
     d, hd, nh, nkv, inter, L, V = a["dim"], a["head_dim"], a["n_head"], a["n_local_heads"], a["intermediate_size"], a["n_layer"], a["vocab_size"]
     per_layer = ((nh + 2 * nkv) * hd * d + nh * hd * d + 3 * inter * d) // t + 2 * d
-    weights = 2 * (L * per_layer + d + V * d)
+    weights = 2 * (L * per_layer + d + V * d // (t if head_split else 1))
     kv = 2 * 2 * L * (nkv // t) * hd * batch * ctx + 2 * 2 * L * (nkv // t) * hd * batch
     return weights + kv
 
@@ -306,8 +310,11 @@ def run_ours(args):
 
     def step():
         with torch.no_grad():
-            lg = model(tok, pos)
-            nxt.copy_(torch.argmax(lg[:, -1], dim=-1, keepdim=True))
+            if args.head == "vocab-parallel":
+                nxt.copy_(model.decode_greedy(tok, pos))
+            else:
+                lg = model(tok, pos)
+                nxt.copy_(torch.argmax(lg[:, -1], dim=-1, keepdim=True))
             tok.copy_(nxt)
             pos.add_(1)
 
@@ -390,7 +397,7 @@ def run_ours(args):
     # ---- dominant kernel, timed alone with CUDA events on the launching stream -------------------------
     roof = dominant_kernel_roofline(model, a, world, B, dtype, dev)
     ctx_mid = T + W + K // 2
-    sb = step_bytes(a, world, B, ctx_mid)
+    sb = step_bytes(a, world, B, ctx_mid, head_split=args.head == "vocab-parallel")
     peak, peak_kind = measured_hbm_peak()
     step_gbs = sb / (ms / K / 1e3) / 1e9
     roof.update({"peak": peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "frac": roof["achieved"] / peak,
@@ -402,7 +409,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": args.dtype, "data": "synthetic",
-        "config": workload_config(args, a, note=f"comm={comm.name}; cuda_graph={graph is not None}"),
+        "config": workload_config(args, a, note=f"comm={comm.name}; cuda_graph={graph is not None}; head={args.head}"),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": B * 4 + 4, "d2h_bytes_per_step": B * 4,
                 "ms_per_step": ms_e2e / K},

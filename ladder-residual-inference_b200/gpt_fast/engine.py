@@ -73,6 +73,13 @@ class Engine:
         # wo and w2 may run at the same time on two streams: one workspace each (w2's also serves the LM head)
         self.ws_wo = workspace(self.ops.linear_workspace_bytes, self.d)
         self.ws_w2 = workspace(self.ops.linear_workspace_bytes, self.d)
+        self.ws_head = workspace(self.ops.linear_workspace_bytes, cfg.vocab_size)
+        # vocabulary-parallel greedy head (decode_greedy): this rank's slice of the output rows
+        self.vocab_per_rank = -(-cfg.vocab_size // (8 * t)) * 8
+        self.vocab_lo = min(cfg.vocab_size, self.comm.rank * self.vocab_per_rank)
+        self.vocab_hi = min(cfg.vocab_size, self.vocab_lo + self.vocab_per_rank)
+        self.head_logits = torch.empty(max_batch * self.vocab_per_rank, dtype=dtype, device=device)
+        self.head_best = torch.empty(t, max_batch, 2, dtype=torch.float32, device=device)
         nbytes = self.ops.attn_decode_scratch_bytes(max_batch, self.nh, self.nkv, self.hd, _MAX_SPLITS)
         self.scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
         # ladder decode runs the attention and MLP chains of a layer on two streams (LRI_LADDER_OVERLAP=0: one)
@@ -125,8 +132,8 @@ class Engine:
         return self.comm.all_reduce_async(buf, rows)
 
     # ------------------------------------------------------------------------------------------
-    @torch.no_grad()
-    def forward(self, idx, input_pos):
+    def _trunk(self, idx, input_pos):
+        """Everything up to the final norm; leaves the normalised hidden states in self.normed."""
         assert self.ready, "Caches must be initialized first"
         B, S = idx.shape
         assert input_pos.shape[0] == S, "input_pos must hold one position per token column"
@@ -137,9 +144,50 @@ class Engine:
         self._splits = decode_splits(B, self.nh, self.nkv, self.model.max_seq_length) if S == 1 else 1
         self.ops.embedding(self.model.tok_embeddings.weight, idx, self.resid)
         getattr(self, "_run_" + self.family)(rows, B, S, input_pos)
+        return B, S, rows
+
+    @torch.no_grad()
+    def forward(self, idx, input_pos):
+        B, S, rows = self._trunk(idx, input_pos)
         logits = torch.empty(B, S, self.cfg.vocab_size, dtype=self.resid.dtype, device=self.resid.device)
-        self.ops.linear(self.normed, self.model.output.weight, logits, rows)
+        self.ops.linear(self.normed, self.model.output.weight, logits, rows, workspace=self.ws_head)
         return logits
+
+    @torch.no_grad()
+    def forward_greedy(self, idx, input_pos):
+        """Decode step that returns the arg-max token of every sequence, int32 [B, 1], instead of logits.
+
+        The output projection is replicated on every rank (reference gpt_fast/gpt_ladder_TP.py:218, 283),
+        and streaming all of it is the largest single item of a decode step at high TP.  Here rank r
+        multiplies only rows [r V/t, (r+1) V/t) of its copy, takes the arg-max of its slice, and the
+        ranks exchange one (value, index) pair per sequence.  The logits of a row do not depend on
+        which other rows are computed, so the token is the one `forward(...).argmax(-1)` gives
+        (lowest index on ties), on every rank.
+        """
+        import torch.distributed as dist
+        B, S, rows = self._trunk(idx, input_pos)
+        assert S == 1, "forward_greedy is a decode step (one position per sequence)"
+        n = self.vocab_hi - self.vocab_lo
+        t = self.comm.world
+        mine = self.head_best[self.comm.rank, :B]
+        if n > 0:
+            local = self.head_logits[: B * n].view(B, n)
+            self.ops.linear(self.normed, self.model.output.weight[self.vocab_lo:self.vocab_hi], local, B,
+                            workspace=self.ws_head)
+            val, ix = local.float().max(dim=-1)
+            mine[:, 0] = val
+            mine[:, 1] = ix + self.vocab_lo  # exact in fp32: vocabularies are far below 2**24
+        else:
+            mine[:, 0] = float("-inf")
+            mine[:, 1] = 0
+        if t == 1:
+            return mine[:, 1].to(torch.int32).view(B, 1)
+        best = self.head_best[:, :B].contiguous() if B != self.max_batch else self.head_best
+        dist.all_gather_into_tensor(best.view(-1), mine.contiguous().view(-1))
+        vals, ids = best[..., 0], best[..., 1]
+        top = vals.max(dim=0).values
+        winner = torch.where(vals == top, ids, torch.full_like(ids, float("inf"))).min(dim=0).values
+        return winner.to(torch.int32).view(B, 1)
 
     # Each _run_* leaves RMSNorm(final residual) * norm.weight in self.normed.
     def _run_ladder(self, rows, B, S, pos):

@@ -66,6 +66,13 @@ def main():
                 err = gu.rel_err(steps, ref)
                 assert err < tol, f"{key} rank {rank}: {err}"
                 assert gu.rel_err(prefill_row0, gold[key + "/prefill_row0"]) < tol
+            if family != "desync":
+                # vocabulary-parallel greedy head: same token as the arg-max of the replicated logits
+                fed = torch.from_numpy(gold[key + "/fed"])
+                n = gu.NEW - 2
+                tok = model.decode_greedy(fed[:, n:n + 1], torch.tensor([gu.PROMPT + n], dtype=torch.int32))
+                want = steps[-1].argmax(-1).to(torch.int32).view(-1, 1)
+                assert torch.equal(tok, want), f"{key} rank {rank}: greedy {tok.flatten().tolist()} vs {want.flatten().tolist()}"
     dist.barrier()
     if rank == 0:
         print("ENGINE-CPU-OK")

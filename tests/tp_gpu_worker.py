@@ -95,6 +95,16 @@ def check_models(comm_name, split=True):
                     assert err < 2e-2, f"{comm_name} {key} rank {rank}: rel err vs bf16 oracle {err:.3e}"
                     far = gu.rel_err(steps, ref)
                     assert far < 1.5 * gu.rel_err(osteps, ref) + 1e-2, f"{comm_name} {key}: {far:.3e} from the fp32 run"
+            if family != "desync":
+                # vocabulary-parallel greedy head: same token as the arg-max of the replicated logits
+                fed = torch.from_numpy(gold[key + "/fed"])
+                n = gu.NEW - 2
+                with torch.no_grad():
+                    tok = model.decode_greedy(fed[:, n:n + 1].to(dev), torch.tensor([gu.PROMPT + n], dtype=torch.int32,
+                                                                                     device=dev))
+                want = steps[-1].argmax(-1).to(torch.int32).view(-1, 1)
+                assert torch.equal(tok.cpu(), want), f"{comm_name} {key} rank {rank}: greedy {tok.flatten().tolist()} " \
+                                                     f"vs arg-max {want.flatten().tolist()}"
             model._engine.comm.status()
     os.environ["LRI_SPLIT_AR"] = "1"
     log(f"models ok with comm={comm_name} split={split}")
