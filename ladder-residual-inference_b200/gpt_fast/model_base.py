@@ -101,7 +101,7 @@ class TPModelBase(nn.Module):
         """Arg-max next token of every sequence, int32 [B, 1]; equal to
         `forward(idx, input_pos)[:, -1].argmax(-1)` but with the output projection split by
         vocabulary over the tensor-parallel ranks (no counterpart in the reference, which
-        samples from the replicated logits, benchmark.py:58-77)."""
+        samples from the replicated logits, benchmark.py:74-92)."""
         assert self.freqs_cis is not None, "Caches must be initialized first"
         return self._engine.forward_greedy(idx, input_pos)
 
