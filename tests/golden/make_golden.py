@@ -163,7 +163,7 @@ def _module_goldens(utils):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     for world in (1, 2):
         cases = [c for c in CASES if c[2] == world]

@@ -32,7 +32,7 @@ def resolve(kw, desync):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     a = ap.parse_args()
     out = {}
     for family in ("ladder", "dense", "parallel", "desync"):
