@@ -89,6 +89,13 @@ int lri_embedding(int dtype, const void* table, const void* idx, int idx_is_i64,
  * lri_qkv_rope_kvcache, lri_gateup_swiglu) may be in flight at once.  Replaces: self.wo / self.w2 / self.output nn.Linear calls, gpt_fast/utils.py:148,
  * 258, 384-385 and gpt_fast/gpt_ladder_TP.py:283. */
 size_t lri_linear_workspace_bytes(int64_t M, int N);
+/* How the stream-K kernel would cut a projection with N outputs (for lri_gateup_swiglu: N = I) and
+ * depth K at 1 <= M <= 64 token rows: 128-output tiles, 64-element K tiles, the number of
+ * persistent CTAs, the most segments one tile may be cut into (the workspace holds that many
+ * fp32 partial tiles of token_tile x 128 per tile) and the token tile 16 / 32 / 64.  Host
+ * arithmetic only, usable without a GPU.  No counterpart in the reference. */
+int lri_streamk_plan(int64_t M, int N, int K, int* tiles, int* k_tiles, int* max_segments, int* ctas,
+                     int* token_tile);
 int lri_linear(int dtype, const void* x, const void* w, const void* addend, void* y, int64_t M,
                int N, int K, void* workspace, size_t workspace_bytes, lri_stream_t stream);
 

@@ -321,6 +321,18 @@ int max_segments(int tiles) {
   return s < kMaxSplitK ? s : kMaxSplitK;
 }
 
+// CTAs of the GEMM kernel: one per SM, fewer when the projection is so small that a CTA would get
+// less than q_min K tiles.  q_min K tiles per CTA bound the CTAs that can share one tile (a tile
+// is total_kt consecutive units) by ceil(total_kt / q_min) + 1 <= max_seg, the capacity of the
+// partial-tile workspace; the kernels rely on it.
+int plan_ctas(int tiles, int total_kt, int max_seg) {
+  const int64_t units = static_cast<int64_t>(tiles) * total_kt;
+  const int q_min = (total_kt + max_seg - 2) / (max_seg - 1);
+  int64_t ctas = units / q_min;
+  ctas = ctas < 1 ? 1 : (ctas > sm_count() ? sm_count() : ctas);
+  return static_cast<int>(ctas);
+}
+
 template <typename T, int BN, int EPI>
 int launch(int dtype, const LinearParams& lin, float* partial, cudaStream_t st) {
   constexpr int kAcc = Acc<EPI>::kCount;
@@ -346,11 +358,7 @@ int launch(int dtype, const LinearParams& lin, float* partial, cudaStream_t st) 
     LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
     attr_set = true;
   }
-  // Every CTA gets at least q_min K tiles, which bounds the segments of a tile by max_seg.
-  const int64_t units = static_cast<int64_t>(p.tiles) * p.total_kt;
-  const int q_min = (p.total_kt + p.max_seg - 2) / (p.max_seg - 1);
-  int64_t ctas = units / q_min;
-  ctas = ctas < 1 ? 1 : (ctas > sm_count() ? sm_count() : ctas);
+  const int64_t ctas = plan_ctas(p.tiles, p.total_kt, p.max_seg);
   p.ctas = static_cast<int>(ctas);
   LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tw, tx,
                       p));
@@ -399,6 +407,17 @@ int gemm_streamk_launch(int dtype, int epi, const LinearParams& lin, void* works
   float* partial = static_cast<float*>(workspace);
   return dtype == LRI_BF16 ? launch_bn<__nv_bfloat16>(dtype, epi, lin, partial, st)
                            : launch_bn<__half>(dtype, epi, lin, partial, st);
+}
+
+// The partition a launch would use (host arithmetic only; lets the plan be checked without a GPU).
+void gemm_streamk_plan(int epi, int64_t m, int n, int k, int* tiles, int* k_tiles, int* max_seg, int* ctas,
+                       int* token_tile_out) {
+  (void)epi;
+  *tiles = tiles_of(n);
+  *k_tiles = (k + kBK - 1) / kBK;
+  *max_seg = max_segments(*tiles);
+  *ctas = plan_ctas(*tiles, *k_tiles, *max_seg);
+  *token_tile_out = token_tile(m);
 }
 
 int gemm_streamk_status_read_and_clear(int* status_out) {

@@ -104,6 +104,8 @@ bool gemm_streamk_supports(int epi, const LinearParams& lin, const void* workspa
 int gemm_streamk_launch(int dtype, int epi, const LinearParams& lin, void* workspace, size_t workspace_bytes,
                         cudaStream_t st);
 int gemm_streamk_status_read_and_clear(int* status_out);
+void gemm_streamk_plan(int epi, int64_t m, int n, int k, int* tiles, int* k_tiles, int* max_seg, int* ctas,
+                       int* token_tile_out);
 
 // elementwise epilogues used after the GEMM on the prefill path
 int swiglu_rows_launch(int dtype, const void* ug /*[m, 2n]*/, void* h /*[m, n]*/, int64_t m, int n, cudaStream_t st);

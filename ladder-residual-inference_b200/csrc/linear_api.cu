@@ -295,6 +295,15 @@ extern "C" int lri_linear(int dtype, const void* x, const void* w, const void* a
   return add_rows_launch(dtype, y, addend, M * N, st);
 }
 
+extern "C" int lri_streamk_plan(int64_t M, int N, int K, int* tiles, int* k_tiles, int* max_segments, int* ctas,
+                                int* token_tile) {
+  LRI_REQUIRE(M >= 1 && M <= kSplitKMaxRows && N >= 1 && K >= 1, LRI_ERR_ARG, "streamk_plan: M=%lld N=%d K=%d",
+              (long long)M, N, K);
+  LRI_REQUIRE(tiles && k_tiles && max_segments && ctas && token_tile, LRI_ERR_ARG, "streamk_plan: NULL output");
+  gemm_streamk_plan(EPI_PLAIN, M, N, K, tiles, k_tiles, max_segments, ctas, token_tile);
+  return LRI_OK;
+}
+
 extern "C" size_t lri_linear_workspace_bytes(int64_t M, int N) { return M < 0 || N <= 0 ? 0 : streamk_bytes(EPI_PLAIN, M, N); }
 
 static size_t gateup_raw_bytes(int64_t M, int I) {

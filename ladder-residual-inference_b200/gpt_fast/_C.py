@@ -41,6 +41,7 @@ _SIGNATURES = {
                                      c_void_p, c_size_t, c_void_p]),
     "lri_gateup_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "lri_linear_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "lri_streamk_plan": (c_int, [c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "lri_gateup_swiglu": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t,
                                   c_void_p]),
     "lri_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),

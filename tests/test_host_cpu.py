@@ -38,6 +38,59 @@ def test_argument_checks_need_no_gpu():
     assert _C.lib.lri_gateup_workspace_bytes(100, 512) == 100 * 1024 * 2
 
 
+def _streamk_plan(M, N, K):
+    import ctypes
+    from gpt_fast import _C
+    out = [ctypes.c_int() for _ in range(5)]
+    _C.check(_C.lib.lri_streamk_plan(M, N, K, *[ctypes.byref(o) for o in out]))
+    return [o.value for o in out]
+
+
+@pytest.mark.parametrize("N", [8, 128, 136, 1000, 4096, 6144, 14336, 28672, 53248, 128256])
+@pytest.mark.parametrize("K", [8, 64, 72, 512, 4096, 14336, 53248])
+def test_streamk_plan_keeps_every_tile_within_its_workspace(N, K):
+    """The kernel deals (tile, K tile) pairs out to CTAs in equal contiguous runs and stores the
+    piece of a tile that a CTA holds in slot (CTA - first CTA of the tile) of the tile's workspace.
+    For every shape the plan must keep that slot below the capacity it sized the workspace for, every
+    CTA must get work, and the pieces of a tile must add up to its whole K range."""
+    from gpt_fast import _C
+    for M in (9, 16, 33, 64):
+        tiles, kt, max_seg, ctas, tok = _streamk_plan(M, N, K)
+        assert tiles == -(-N // 128) and kt == -(-K // 64) and tok == (16 if M <= 16 else 32 if M <= 32 else 64)
+        assert 2 <= max_seg <= 8 and 1 <= ctas <= 148
+        assert _C.lib.lri_linear_workspace_bytes(M, N) == tiles * max_seg * tok * 128 * 4
+        assert _C.lib.lri_gateup_workspace_bytes(M, N) == 2 * tiles * max_seg * tok * 128 * 4
+    units = tiles * kt
+    start = [units * b // ctas for b in range(ctas + 1)]            # the kernel's unit_start()
+    cta_of = lambda u: ((u + 1) * ctas - 1) // units                # the kernel's cta_of_unit()
+    assert all(start[b + 1] > start[b] for b in range(ctas))
+    covered = [0] * tiles
+    for b in range(ctas):
+        u = start[b]
+        while u < start[b + 1]:
+            t, k0 = divmod(u, kt)
+            nk = min(kt - k0, start[b + 1] - u)
+            first, last = cta_of(t * kt), cta_of((t + 1) * kt - 1)
+            assert first <= b <= last and last - first + 1 <= max_seg, (N, K, b, t, first, last, max_seg)
+            covered[t] += nk
+            u += nk
+    assert covered == [kt] * tiles
+
+
+def test_workspace_sizes():
+    from gpt_fast import _C
+    lib = _C.lib
+    # up to 8 rows: streaming kernels, no workspace; 9..64: stream-K partial tiles; above: raw projection
+    assert lib.lri_linear_workspace_bytes(8, 4096) == 0 and lib.lri_linear_workspace_bytes(65, 4096) == 0
+    assert lib.lri_linear_workspace_bytes(9, 4096) == lib.lri_linear_workspace_bytes(16, 4096) > 0
+    assert lib.lri_gateup_workspace_bytes(8, 14336) == 0
+    assert lib.lri_gateup_workspace_bytes(16, 14336) == 112 * 3 * 2 * 16 * 128 * 4
+    assert lib.lri_qkv_workspace_bytes(16, 32, 8, 128) == 48 * 5 * 16 * 128 * 4
+    assert lib.lri_qkv_workspace_bytes(65, 32, 8, 128) == 65 * 48 * 128 * 2
+    rc = lib.lri_streamk_plan(65, 4096, 4096, None, None, None, None, None)
+    assert rc == -1
+
+
 def test_no_cpu_fallback():
     """The product must refuse CPU tensors instead of computing somewhere else."""
     from gpt_fast.utils import RMSNorm
