@@ -4,6 +4,8 @@
 tensors and raises otherwise.  The engine takes the ops object as a parameter so that host-side
 schedule logic can be exercised by tests with a stand-in.
 """
+import os
+
 import torch
 
 from . import _C
@@ -102,6 +104,9 @@ def decode_splits(B, n_head, n_kv, smax, sm_count=148, head_dim=128):
     thread-block cluster and merge through shared memory; that form is kept as long as a CTA
     then streams at most ~1 MB of K/V.  Longer caches take more ranges (up to 64, at least 64
     positions each) and merge through the scratch buffer."""
+    forced = os.environ.get("LRI_DECODE_SPLITS")  # tuning knob
+    if forced:
+        return max(1, min(64, int(forced), max(1, smax // 32)))
     g = n_head // n_kv
     gt = 4 if g % 4 == 0 else (2 if g % 2 == 0 else 1)
     base = max(1, B * n_kv * (g // gt))
