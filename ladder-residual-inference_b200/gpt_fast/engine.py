@@ -189,6 +189,62 @@ class Engine:
         winner = torch.where(vals == top, ids, torch.full_like(ids, float("inf"))).min(dim=0).values
         return winner.to(torch.int32).view(B, 1)
 
+    @torch.no_grad()
+    def forward_sample(self, idx, input_pos, temperature=1.0, top_k=None, generator=None):
+        """Decode step that returns one sampled token per sequence, int32 [B, 1], from the reference's
+        sampling rule (benchmark.py:56-77: logits / max(temperature, 1e-5), optional top-k cut at the
+        k-th largest value, softmax, argmax(probs / q) with q ~ Exponential(1)), with the output
+        projection split by vocabulary as in forward_greedy.
+
+        Every rank draws the same [B, V] noise (same generator state on every rank, as the reference
+        seeds its ranks alike) and uses its slice, so all ranks return the same token.  The k-th
+        largest value comes from the ranks' local top-k lists, the softmax normaliser from an
+        all-reduce of the local maxima and sums; probabilities are rounded to the model type as the
+        reference's softmax output is, so the draw is the reference's up to the rounding of the
+        normaliser (summation order differs)."""
+        import torch.distributed as dist
+        B, S, rows = self._trunk(idx, input_pos)
+        assert S == 1, "forward_sample is a decode step (one position per sequence)"
+        t, V = self.comm.world, self.cfg.vocab_size
+        n = self.vocab_hi - self.vocab_lo
+        dtype, dev = self.resid.dtype, self.resid.device
+        local = self.head_logits[: B * max(n, 1)].view(B, max(n, 1))
+        if n > 0:
+            self.ops.linear(self.normed, self.model.output.weight[self.vocab_lo:self.vocab_hi], local, B,
+                            workspace=self.ws_head)
+            x = local / max(temperature, 1e-5)
+        else:
+            x = torch.full((B, 1), float("-inf"), dtype=dtype, device=dev)
+
+        def gathered(v):  # [B, c] on every rank -> [t, B, c]
+            if t == 1:
+                return v.unsqueeze(0)
+            out = torch.empty((t,) + tuple(v.shape), dtype=v.dtype, device=dev)
+            dist.all_gather_into_tensor(out.view(-1), v.contiguous().view(-1))
+            return out
+
+        if top_k is not None:
+            k = min(top_k, V)
+            mine = torch.full((B, k), float("-inf"), dtype=dtype, device=dev)
+            kl = min(k, x.shape[1])
+            mine[:, :kl] = torch.topk(x, kl).values
+            cand = gathered(mine).permute(1, 0, 2).reshape(B, t * k)
+            kth = torch.topk(cand, k).values[:, -1:]
+            x = torch.where(x < kth, torch.full_like(x, float("-inf")), x)
+        xf = x.float()
+        top = gathered(xf.max(dim=-1, keepdim=True).values).max(dim=0).values          # [B, 1]
+        e = torch.exp(xf - top)
+        total = gathered(e.sum(dim=-1, keepdim=True)).sum(dim=0)                        # [B, 1], rank order
+        probs = (e / total).to(dtype)
+        q = torch.empty(B, V, dtype=dtype, device=dev).exponential_(1, generator=generator)
+        score = (probs / q[:, self.vocab_lo:self.vocab_lo + x.shape[1]]).float() if n > 0 else xf
+        val, ix = score.max(dim=-1)
+        mine = torch.stack([val, (ix + self.vocab_lo).float()], dim=-1)                 # [B, 2]
+        best = gathered(mine)
+        vals, ids = best[..., 0], best[..., 1]
+        win = torch.where(vals == vals.max(dim=0).values, ids, torch.full_like(ids, float("inf"))).min(dim=0).values
+        return win.to(torch.int32).view(B, 1)
+
     # Each _run_* leaves RMSNorm(final residual) * norm.weight in self.normed.
     def _run_ladder(self, rows, B, S, pos):
         if S == 1 and self.overlap_sublayers:

@@ -105,6 +105,14 @@ class TPModelBase(nn.Module):
         assert self.freqs_cis is not None, "Caches must be initialized first"
         return self._engine.forward_greedy(idx, input_pos)
 
+    def decode_sample(self, idx: Tensor, input_pos: Tensor, temperature: float = 1.0, top_k: Optional[int] = None,
+                      generator=None) -> Tensor:
+        """One sampled next token per sequence, int32 [B, 1], by the reference's rule
+        (`sample(model(idx, input_pos), temperature, top_k)[0]`, benchmark.py:56-92), computed on the
+        vocabulary-split output projection; see Engine.forward_sample."""
+        assert self.freqs_cis is not None, "Caches must be initialized first"
+        return self._engine.forward_sample(idx, input_pos, temperature, top_k, generator)
+
 
 class BlockBase(nn.Module):
     def extra_repr(self) -> str:

@@ -379,3 +379,17 @@ def greedy_generate(model: OracleModel, prompt: torch.Tensor, batch: int, new_to
         tok = logits[:, -1].float().argmax(dim=-1, keepdim=True)
         toks.append(tok)
     return torch.cat(toks, dim=-1), steps
+
+
+def sample(logits: torch.Tensor, temperature: float = 1.0, top_k=None, generator=None):
+    """benchmark.py:56-77 on last-position logits [B, V]: divide by max(temperature, 1e-5); with top_k,
+    everything below the k-th largest value of a row becomes -inf; softmax; then one draw per row as
+    argmax(probs / q) with q ~ Exponential(1) of the shape and type of probs.  Returns (int32 [B, 1], probs)."""
+    x = logits / max(temperature, 1e-5)
+    if top_k is not None:
+        kth = torch.topk(x, min(top_k, x.size(-1))).values[..., -1:]
+        x = torch.where(x < kth, torch.full_like(x, float("-inf")), x)
+    probs = torch.nn.functional.softmax(x, dim=-1)
+    q = torch.empty_like(probs).exponential_(1, generator=generator)
+    return torch.argmax(probs / q, dim=-1, keepdim=True).to(torch.int32), probs
+

@@ -73,6 +73,14 @@ def main():
                 tok = model.decode_greedy(fed[:, n:n + 1], torch.tensor([gu.PROMPT + n], dtype=torch.int32))
                 want = steps[-1].argmax(-1).to(torch.int32).view(-1, 1)
                 assert torch.equal(tok, want), f"{key} rank {rank}: greedy {tok.flatten().tolist()} vs {want.flatten().tolist()}"
+                # vocabulary-parallel sampling: the reference's rule on the full logits, same noise
+                last = steps[-1].to(dtype)
+                for temperature, top_k in ((1.0, None), (0.7, 5), (1.3, 40), (1.0, 1), (1.0, 10 ** 6)):
+                    got = model.decode_sample(fed[:, n:n + 1], torch.tensor([gu.PROMPT + n], dtype=torch.int32),
+                                              temperature, top_k, generator=torch.Generator().manual_seed(11))
+                    ref_tok, _ = lo.sample(last, temperature, top_k, generator=torch.Generator().manual_seed(11))
+                    assert torch.equal(got, ref_tok), f"{key} rank {rank} T={temperature} k={top_k}: " \
+                                                      f"{got.flatten().tolist()} vs {ref_tok.flatten().tolist()}"
     dist.barrier()
     if rank == 0:
         print("ENGINE-CPU-OK")
