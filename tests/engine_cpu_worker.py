@@ -25,6 +25,44 @@ from gpt_fast import gpt_dense_TP, gpt_desync_TP, gpt_ladder_TP, gpt_parallel_TP
 from gpt_fast.comm import make_comm  # noqa: E402
 
 
+def check_hf_checkpoint(rank, world, mods):
+    """A small random Hugging Face Llama, saved as safetensors, loaded shard by shard into the
+    drop-in dense and ladder models; the dense logits must be transformers' own."""
+    import tempfile
+    try:
+        import transformers
+        from safetensors.torch import save_file
+    except ImportError:
+        return
+    from gpt_fast.loader import load_hf_checkpoint
+    hcfg = transformers.LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, rope_theta=500000.0, rms_norm_eps=1e-5,
+                                    max_position_embeddings=512, tie_word_embeddings=False)
+    torch.manual_seed(3)
+    hf = transformers.LlamaForCausalLM(hcfg).eval()
+    ids = torch.randint(0, 512, (2, 12), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = hf(ids).logits
+    with tempfile.TemporaryDirectory() as tmp:
+        sd = {k: v.contiguous() for k, v in hf.state_dict().items()}
+        save_file(sd, f"{tmp}/model-rank{rank}.safetensors")
+        kw = dict(block_size=512, vocab_size=512, n_layer=2, n_head=4, n_local_heads=2, dim=256, intermediate_size=512,
+                  rope_base=500000, norm_eps=1e-5)
+        for family in ("dense", "ladder"):
+            mod, cls = mods[family]
+            mod.transformer_configs["tiny-hf"] = dict(kw)
+            model = cls.from_name("tiny-hf").to(torch.float32).eval()
+            load_hf_checkpoint(model, f"{tmp}/model-rank{rank}.safetensors")
+            model.setup_caches(max_batch_size=2, max_seq_length=16)
+            model._engine.ops = CpuOps
+            got = model(ids, torch.arange(12))
+            if family == "dense":
+                err = ((got - want).abs().max() / want.abs().max()).item()
+                assert err < 2e-5, f"hf checkpoint, rank {rank}: {err}"
+            else:  # a different schedule on the same weights: finite and not the dense logits
+                assert torch.isfinite(got).all() and (got - want).abs().max() > 1e-3
+
+
 def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     mods = {"ladder": (gpt_ladder_TP, gpt_fast.GPTLadder), "dense": (gpt_dense_TP, gpt_fast.GPTDense),
@@ -81,6 +119,7 @@ def main():
                     ref_tok, _ = lo.sample(last, temperature, top_k, generator=torch.Generator().manual_seed(11))
                     assert torch.equal(got, ref_tok), f"{key} rank {rank} T={temperature} k={top_k}: " \
                                                       f"{got.flatten().tolist()} vs {ref_tok.flatten().tolist()}"
+    check_hf_checkpoint(rank, world, mods)
     dist.barrier()
     if rank == 0:
         print("ENGINE-CPU-OK")
