@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--head", default="replicated", choices=["replicated", "vocab-parallel"],
                     help="vocab-parallel: greedy choice through model.decode_greedy (output rows split over the ranks); "
                          "replicated (default) is the reference's scheme")
+    ap.add_argument("--steps-per-replay", type=int, default=1,
+                    help="decode steps captured into one CUDA graph (token feedback and position stay on the device); "
+                         "--steps must be a multiple")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly (for kernel profiling)")
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers in the CPU sample")
@@ -288,7 +291,9 @@ def run_ours(args):
         for p in model.parameters():
             torch.nn.init.normal_(p, mean=0.0, std=0.02)
     B, T, K, W = args.batch, args.prompt, args.steps, args.warmup
-    total_steps = 2 * (W + K) + 16
+    spr = args.steps_per_replay if not args.no_graph else 1
+    assert K % spr == 0, "--steps must be a multiple of --steps-per-replay"
+    total_steps = 2 * (W * spr + K) + 16 + 4 * spr
     model.setup_caches(max_batch_size=B, max_seq_length=min(T + total_steps, model.config.block_size))
     comm = make_comm()
 
@@ -335,7 +340,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            step()
+            for _ in range(spr):
+                step()
     run = graph.replay if graph is not None else step
 
     def reset():
@@ -361,11 +367,12 @@ def run_ours(args):
     for _ in range(W):
         run()
     sampler = ClockSampler(torch.cuda.current_device())
+    K_runs = K // spr
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
     t_wall0 = time.time()
-    ms = timed(K, run)
+    ms = timed(K_runs, run)
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     value = B * K / (ms / 1e3)
@@ -385,12 +392,12 @@ def run_ours(args):
         h_next.copy_(nxt, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         h_tok.copy_(h_next)
-        state["pos"] += 1
+        state["pos"] += spr
 
     for _ in range(W):
         e2e_step()
-    state["pos"] = T + W
-    ms_e2e = timed(K, e2e_step)
+    state["pos"] = T + W * spr
+    ms_e2e = timed(K_runs, e2e_step)
     e2e_value = B * K / (ms_e2e / 1e3)
     comm.status()
 
@@ -409,9 +416,9 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": args.dtype, "data": "synthetic",
-        "config": workload_config(args, a, note=f"comm={comm.name}; cuda_graph={graph is not None}; head={args.head}"),
+        "config": workload_config(args, a, note=f"comm={comm.name}; cuda_graph={graph is not None}; head={args.head}; steps_per_replay={spr}"),
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": B * 4 + 4, "d2h_bytes_per_step": B * 4,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": (B * 4 + 4) / spr, "d2h_bytes_per_step": B * 4 / spr,
                 "ms_per_step": ms_e2e / K},
         "gpu_launches": int(launches_per_step * K),
         "launches_per_step": int(launches_per_step),

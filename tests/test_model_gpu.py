@@ -181,6 +181,39 @@ def test_decode_greedy_and_decode_sample_match_the_rule_on_the_logits(family):
             assert torch.equal(got.cpu(), want.cpu()), f"T={temperature} k={top_k}"
 
 
+@pytest.mark.parametrize("head", ["replicated", "vocab-parallel"])
+def test_device_loop_matches_step_by_step_greedy(head):
+    """generate.DeviceLoop (several decode steps per graph replay, token feedback and position on the
+    device) must produce the tokens of a host-driven greedy loop."""
+    from gpt_fast.generate import DeviceLoop
+    gold = gu.load(1)
+    family, key = "ladder", "ladder-bfloat16-tp1-loud"
+    cfg = gu.tiny_config(family)
+    full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS["loud"])
+    n_new = 7
+    prompt = torch.from_numpy(gold[key + "/prompt"])
+    x = prompt.view(1, -1).repeat(gu.BATCH, 1).cuda()
+
+    def prefill(model):
+        with torch.no_grad():
+            return model(x, torch.arange(gu.PROMPT, device="cuda"))[:, -1].argmax(-1, keepdim=True).to(torch.int32)
+
+    model = build_model(family, cfg, full, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1)
+    first = prefill(model)
+    want, tok = [], first
+    with torch.no_grad():
+        for n in range(n_new):
+            tok = model(tok, torch.tensor([gu.PROMPT + n], dtype=torch.int32, device="cuda"))[:, -1].argmax(-1, keepdim=True)
+            want.append(tok.to(torch.int32))
+    want = torch.cat(want, dim=1).cpu()
+
+    model2 = build_model(family, cfg, full, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1, name="test-preset-loop")
+    loop = DeviceLoop(model2, gu.BATCH, steps_per_replay=4, head=head)
+    loop.start(prefill(model2), gu.PROMPT)
+    got = loop.run(n_new).cpu()
+    assert torch.equal(got, want), f"{got.tolist()} vs {want.tolist()}"
+
+
 def test_module_level_forward_matches_engine():
     """The reference's block-level interface (blocks driven by hand with gathered RoPE rows and a
     mask) gives the same logits as the engine's whole-model forward."""
