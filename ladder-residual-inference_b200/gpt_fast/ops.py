@@ -108,6 +108,12 @@ def decode_splits(B, n_head, n_kv, smax, sm_count=148, head_dim=128):
     if forced:
         return max(1, min(64, int(forced), max(1, smax // 32)))
     g = n_head // n_kv
+    mma = os.environ.get("LRI_ATTN_MMA")
+    if g <= 16 and (mma == "1" or (mma is None and B * n_kv >= 128)):
+        # tensor-core kernel (one CTA per sequence, KV head and range; two CTAs per SM): a second
+        # range only while one range per pair would leave SMs without work; more ranges cost more
+        # in the merge than they gain
+        return 2 if (B * n_kv < 2 * sm_count and smax >= 256) else 1
     gt = 4 if g % 4 == 0 else (2 if g % 2 == 0 else 1)
     base = max(1, B * n_kv * (g // gt))
     want = max(1, -(-2 * sm_count // base))

@@ -221,6 +221,34 @@ def test_attn_decode(dtype, B, nh, nkv, hd, pos, splits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,nh,nkv,hd", [(16, 32, 8, 128), (64, 8, 2, 64), (32, 64, 4, 128), (17, 24, 8, 64)])
+@pytest.mark.parametrize("pos", [0, 15, 16, 200, 255])
+def test_attn_decode_many_sequences(dtype, B, nh, nkv, hd, pos):
+    """From 128 (sequence, KV head) pairs on the decode attention runs on tensor cores (the query
+    heads of a KV head are the rows of the tiles); the number of ranges is the engine's choice."""
+    from gpt_fast.ops import decode_splits
+    smax = 256
+    g = torch.Generator().manual_seed(B + nh + pos)
+    q = _randn(g, B, nh, 1, hd, dtype=dtype)
+    kc, vc = _randn(g, B, nkv, smax, hd, dtype=dtype), _randn(g, B, nkv, smax, hd, dtype=dtype)
+    ipos = torch.tensor([pos], dtype=torch.int32)
+    ref = lo.attention_core(q, kc, vc, ipos).transpose(1, 2).reshape(B, nh * hd)
+    ops = _ops()
+    splits = decode_splits(B, nh, nkv, smax)
+    assert splits in (1, 2)
+    scratch = torch.zeros(ops.attn_decode_scratch_bytes(B, nh, nkv, hd, splits), dtype=torch.uint8, device="cuda")
+    out = torch.empty(B, nh * hd, dtype=dtype, device="cuda")
+    for _ in range(2):  # twice: the arrival counters must be back at zero
+        out.fill_(float("nan"))
+        ops.attention(q.view(B, nh * hd).cuda(), kc.cuda(), vc.cuda(), ipos.cuda(), out, B, 1, nh, nkv, hd, scratch,
+                      splits)
+        got = out.float().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - ref.float()).abs().max().item() < 2e-2 * ref.float().abs().max().item() + 1e-3
+        assert gu.rel_err(got, ref) < 6e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,S,pos0", [(1, 12, 0), (2, 64, 0), (1, 65, 0), (2, 130, 7), (1, 300, 0), (1, 2, 100)])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 2, 128)])
 def test_attn_prefill(dtype, B, S, pos0, nh, nkv, hd):
