@@ -91,6 +91,29 @@ def test_workspace_sizes():
     assert rc == -1
 
 
+def test_decode_splits_choice(monkeypatch):
+    """Number of position ranges of decode attention: fixed per cache geometry (never a function of
+    the current position), a power of two up to 8 for the cluster kernel, up to 64 ranges of at
+    least 64 positions for long caches, and one or two ranges once the tensor-core kernel takes over."""
+    from gpt_fast.ops import decode_splits
+    monkeypatch.delenv("LRI_ATTN_MMA", raising=False)
+    monkeypatch.delenv("LRI_DECODE_SPLITS", raising=False)
+    for B in (1, 2, 4, 8):
+        for nh, nkv in ((32, 8), (64, 8), (8, 1), (4, 4)):
+            for smax in (64, 256, 1288, 8192, 131072):
+                n = decode_splits(B, nh, nkv, smax)
+                assert 1 <= n <= 64 and smax // n >= 32
+                assert n in (1, 2, 4, 8) or smax // n >= 64
+    assert decode_splits(1, 32, 8, 1288) == 8          # 8B, batch 1: one cluster of 8 CTAs per head tile
+    assert decode_splits(16, 32, 8, 1288) == 2          # 128 (sequence, KV head) pairs: tensor-core kernel, two ranges
+    assert decode_splits(64, 32, 8, 1288) == 1          # 512 pairs: one range each
+    assert decode_splits(64, 4, 1, 1288) == 4           # TP=8 shard: below 128 pairs, the cluster kernel
+    monkeypatch.setenv("LRI_ATTN_MMA", "0")
+    assert decode_splits(64, 32, 8, 1288) == 1 and decode_splits(16, 32, 8, 1288) == 2   # the cluster kernel's own choice
+    monkeypatch.setenv("LRI_DECODE_SPLITS", "5")
+    assert decode_splits(3, 32, 8, 1288) == 5
+
+
 def test_no_cpu_fallback():
     """The product must refuse CPU tensors instead of computing somewhere else."""
     from gpt_fast.utils import RMSNorm
