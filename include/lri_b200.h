@@ -136,6 +136,11 @@ int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t
  * lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits) bytes, 16-byte aligned;
  * its first 32768 bytes are arrival counters that must be zero before the first call
  * (each call leaves them zero).  Calls sharing one scratch must not overlap on the device.
+ * Three kernels serve this entry point: with 1, 2, 4 or 8 ranges and fewer than 128 (sequence,
+ * KV head) pairs the ranges are the CTAs of one thread-block cluster and merge through
+ * distributed shared memory (scratch untouched); from 128 pairs on (and n_head / n_kv <= 16) a
+ * tensor-core kernel takes the query heads of a KV head as the rows of mma tiles and merges the
+ * ranges through the scratch; other range counts use the SIMT scratch kernel.
  * Replaces: the decode case of gpt_fast/utils.py:252-255 (repeat_interleave + SDPA over the
  * whole cache under mask = causal_mask[input_pos]). */
 size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int head_dim, int num_splits);
