@@ -114,6 +114,24 @@ def test_decode_splits_choice(monkeypatch):
     assert decode_splits(3, 32, 8, 1288) == 5
 
 
+def test_bench_roofline_arithmetic():
+    """Algorithmic bytes per decode step and FLOPs per prompt pass, per rank, for the benchmark's
+    shapes: weights once (layer shards, norms, replicated LM head) plus the valid KV cache."""
+    sys.path.insert(0, ROOT)
+    import bench
+    a8, a70 = bench.shape_of("llama-3-8b", "ladder"), bench.shape_of("llama-3-70b", "ladder")
+    assert [round(bench.step_bytes(a8, t, 1, 0) / 1e9, 2) for t in (1, 2, 4, 8)] == [15.01, 8.03, 4.54, 2.80]
+    assert [round(bench.step_bytes(a70, t, 1, 0) / 1e9, 1) for t in (1, 2, 4, 8)] == [139.0, 70.6, 36.3, 19.2]
+    # one cached position of one sequence, all ranks: 2 (K, V) * L * n_kv * hd * 2 bytes
+    assert bench.step_bytes(a8, 1, 1, 1) - bench.step_bytes(a8, 1, 1, 0) == 131072
+    assert bench.step_bytes(a70, 1, 1, 1) - bench.step_bytes(a70, 1, 1, 0) == 327680
+    # vocabulary-parallel head: the LM head's bytes divide by the ranks
+    full, split = bench.step_bytes(a8, 8, 1, 0), bench.step_bytes(a8, 8, 1, 0, head_split=True)
+    assert full - split == 2 * 128256 * 4096 * 7 // 8
+    # prompt pass of 32 x 4096 tokens at TP=8: projections + causal attention + LM head on every position
+    assert round(bench.prefill_flops(a8, 8, 32, 4096) / 1e12, 1) == 384.0
+
+
 def test_no_cpu_fallback():
     """The product must refuse CPU tensors instead of computing somewhere else."""
     from gpt_fast.utils import RMSNorm
