@@ -53,6 +53,18 @@ const char* lri_last_error(void);
 int lri_version(void);
 /* Selects the GEMM back end used by the linear-layer entry points (process-wide). */
 int lri_set_gemm_backend(int backend);
+/* Tuning options: one table per process, each entry initialised from an LRI_* environment variable
+ * at first use and changeable at run time; a change applies from the next launch on.  Names (initial
+ * value from): stream_rows (LRI_STREAM_ROWS, 1..16, token rows up to which the weight-streaming
+ * kernels run), gemv_simt (LRI_GEMV_SMALL=simt), gemv_rows_per_cta (LRI_GEMV_R: 0, 2, 4, 8),
+ * gemv_depth (LRI_GEMV_U: 0, 2), gemv_mma_tiles (LRI_GEMV_MT: 0, 1, 2, 4), gemm_group
+ * (LRI_GEMM_GROUP), fused_prefill (LRI_FUSED_PREFILL: 0, 1), pdl (LRI_PDL: 0, 1), attn_cluster
+ * (LRI_ATTN_CLUSTER: 0, 1), attn_mma (LRI_ATTN_MMA: -1 choose, 0, 1), decode_splits
+ * (LRI_DECODE_SPLITS: 0 choose, 1..64), fused_norm (LRI_FUSED_NORM: -1 choose, 0, 1).  Unknown
+ * names and values an option does not take return LRI_ERR_ARG.  No counterpart in the reference
+ * (its only switches are benchmark.py's command-line flags). */
+int lri_set_option(const char* name, int value);
+int lri_get_option(const char* name, int* value_out);
 /* Number of kernels this library has launched from the calling process so far. */
 int64_t lri_launch_count(void);
 /* The tcgen05 GEMM bounds every mbarrier wait; a wait that gives up records its site in a
@@ -144,6 +156,10 @@ int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t
  * Replaces: the decode case of gpt_fast/utils.py:252-255 (repeat_interleave + SDPA over the
  * whole cache under mask = causal_mask[input_pos]). */
 size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int head_dim, int num_splits);
+/* The num_splits the library recommends for a cache geometry (host arithmetic on the SM count of the
+ * current device, 148 without one; honours the decode_splits and attn_mma options): fixed per
+ * geometry so that a captured graph stays valid as the position grows. */
+int lri_attn_decode_plan(int B, int n_head, int n_kv, int head_dim, int64_t smax, int* num_splits);
 int lri_attn_decode(int dtype, const void* q, const void* k_cache, const void* v_cache,
                     const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
                     int head_dim, int64_t smax, int num_splits, void* scratch,
@@ -222,6 +238,26 @@ int lri_add_rmsnorm_gather(lri_comm* comm, int dtype, const void* residual, int 
                            const void* add1, int channel2, const void* add2, float residual_scale,
                            const void* weight, float eps, void* residual_out, void* normed_out,
                            int64_t rows, int dim, int timeout_ms, lri_stream_t stream);
+/* ---- greedy decoding head: LM-head projection + arg-max over vocabulary rows and ranks ---------
+ * token_out[m] (int32) = index of the largest logit of sequence m over the whole vocabulary, lowest
+ * index on ties, where this rank holds rows [index_offset, index_offset + N) of the output projection
+ * (w [N, K]) and the other ranks of `comm` hold the rest; comm == NULL: one rank.  Logits are compared
+ * as the projection would store them (fp32 sums rounded to `dtype`).  M <= 8: the weight-streaming
+ * kernel folds its candidates in its epilogue and writes no logits; the CTA that finishes last
+ * exchanges one 16-byte line per sequence with every peer over NVLink (bounded wait: timeout_ms,
+ * status word read by lri_comm_status) and writes the winner, so projection, local arg-max, exchange
+ * and global arg-max are one launch.  8 < M <= 64: the slice's logits go to logits_ws (M*N elements)
+ * through lri_linear (workspace as there) and a second small kernel folds and exchanges them.
+ * scratch: lri_lm_head_argmax_scratch_bytes() bytes, 16-byte aligned, zero before the first call;
+ * every call leaves it zero.  All ranks must call with the same M; N may be 0 on a rank whose slice
+ * is empty.  Every rank writes the same tokens.
+ * Replaces: the output projection + sampling at top_k = 1 / arg-max of the logits,
+ * gpt_fast/gpt_ladder_TP.py:282-283 with benchmark.py:56-77, 86-92. */
+size_t lri_lm_head_argmax_scratch_bytes(void);
+int lri_lm_head_argmax(lri_comm* comm, int dtype, const void* x, const void* w, int64_t M, int N, int K,
+                       int64_t index_offset, int32_t* token_out, void* scratch, size_t scratch_bytes,
+                       void* logits_ws, size_t logits_ws_bytes, void* workspace, size_t workspace_bytes,
+                       int timeout_ms, lri_stream_t stream);
 /* Reads (and clears) the device status word: LRI_OK or LRI_ERR_TIMEOUT.  Synchronises `stream`. */
 int lri_comm_status(lri_comm* comm, lri_stream_t stream);
 int lri_comm_destroy(lri_comm* comm);

@@ -13,7 +13,7 @@ constexpr int kMaxVecPerThread = 8;  // 256 threads * 8 vectors * 8 elements = d
 // ranks' low-latency lines (the reduction half of an all-reduce, done where the sum is used).
 template <typename T, bool GATHER>
 __global__ void __launch_bounds__(kNormThreads)
-add_rmsnorm_kernel(const T* __restrict__ residual, const T* __restrict__ add1, const T* __restrict__ add2,
+add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __restrict__ add1, const T* __restrict__ add2,
                    float residual_scale, const T* __restrict__ weight, float eps, T* residual_out,
                    T* __restrict__ normed_out, int dim, const GatherArgs g) {
   const int64_t row = blockIdx.x;

@@ -783,11 +783,8 @@ int launch_decode_mma(const DecodeParams& p, int B, cudaStream_t st) {
   static_assert((kMmaDecMaxGroup * kMaxSplits + kMmaDecMaxGroup) * 4 <= kMmaDecWarps * kMmaDecTile * HD * 4,
                 "the split weights must fit in the value array");
   auto kern = attn_decode_mma_kernel<T, HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_set{0};  // per template instantiation, one bit per device
+  LRI_ONCE_PER_DEVICE(attr_set, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(p.num_splits, p.n_kv, B);
   LRI_CUDA(launch_pdl(kern, grid, dim3(kMmaDecThreads), static_cast<size_t>(smem), st, p));
   LRI_LAUNCH_CHECK("attn_decode_mma_kernel");
@@ -813,11 +810,8 @@ template <typename T, int HD>
 int launch_prefill(const PrefillParams& p, int B, cudaStream_t st) {
   constexpr int smem = (kPfBlockM + 2 * kPfBlockN) * (HD + 8) * 2;
   auto kern = attn_prefill_kernel<T, HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_set{0};  // per template instantiation, one bit per device
+  LRI_ONCE_PER_DEVICE(attr_set, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((p.S + kPfBlockM - 1) / kPfBlockM, p.n_head, B);
   kern<<<grid, kPfThreads, smem, st>>>(p);
   LRI_LAUNCH_CHECK("attn_prefill_kernel");
@@ -828,10 +822,7 @@ int launch_prefill(const PrefillParams& p, int B, cudaStream_t st) {
 // B200 at 8 KV heads, context 1152: batch 16 20.0 vs 24.0 us, batch 64 59 vs 82 us per layer),
 // the latency kernels below that.  LRI_ATTN_MMA=1 / 0 forces / forbids it.
 bool attn_mma_wanted(int B, int n_kv) {
-  static const int mode = [] {
-    const char* e = getenv("LRI_ATTN_MMA");
-    return e ? (atoi(e) == 1 ? 1 : 0) : -1;
-  }();
+  const int mode = option(OPT_ATTN_MMA);
   return mode == 1 || (mode == -1 && static_cast<int64_t>(B) * n_kv >= 128);
 }
 
@@ -862,6 +853,46 @@ extern "C" size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int
   if (B <= 0 || n_head <= 0 || head_dim <= 0 || num_splits <= 0) return 0;
   const size_t rows = static_cast<size_t>(B) * n_head;
   return kCounterBytes + align_up(rows * num_splits * 2 * 4, 16) + rows * num_splits * head_dim * 4;
+}
+
+// Number of sequence ranges, fixed per cache geometry so that the launch grid never depends on the
+// current position.  Up to 8 ranges (a power of two) run as one thread-block cluster and merge
+// through shared memory; that form is kept as long as a CTA then streams at most ~1 MB of K/V.
+// Longer caches take more ranges (up to 64, at least 64 positions each) and merge through the scratch
+// buffer.  The tensor-core kernel (from 128 (sequence, KV head) pairs on) takes one range per pair,
+// two only while one per pair would leave SMs without work.
+extern "C" int lri_attn_decode_plan(int B, int n_head, int n_kv, int head_dim, int64_t smax, int* num_splits) {
+  LRI_REQUIRE(num_splits != nullptr, LRI_ERR_ARG, "attn_decode_plan: NULL output");
+  LRI_REQUIRE(B >= 1 && n_head >= 1 && n_kv >= 1 && n_head % n_kv == 0 && head_dim >= 1 && smax >= 1, LRI_ERR_ARG,
+              "attn_decode_plan: B=%d n_head=%d n_kv=%d head_dim=%d smax=%lld", B, n_head, n_kv, head_dim, (long long)smax);
+  const int64_t sms = device_sm_count();
+  const int forced = option(OPT_DECODE_SPLITS);
+  if (forced > 0) {
+    const int64_t cap = smax / 32 > 1 ? smax / 32 : 1;
+    *num_splits = static_cast<int>(forced < cap ? forced : cap);
+    return LRI_OK;
+  }
+  const int g = n_head / n_kv;
+  if (g <= kMmaDecMaxGroup && attn_mma_wanted(B, n_kv)) {
+    *num_splits = (static_cast<int64_t>(B) * n_kv < 2 * sms && smax >= 256) ? 2 : 1;
+    return LRI_OK;
+  }
+  const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
+  const int64_t base = static_cast<int64_t>(B) * n_kv * (g / gt);
+  const int64_t want = (2 * sms + base - 1) / base;
+  const int64_t bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8;
+  if (want <= 8 || bytes_per_cta_at_8 <= (1 << 20)) {
+    int n = 1;
+    const int64_t lim = want < 8 ? want : 8;
+    while (n * 2 <= lim && smax / (n * 2) >= 32) n *= 2;
+    *num_splits = n;
+    return LRI_OK;
+  }
+  int64_t n = want < 64 ? want : 64;
+  const int64_t by_len = smax / 64 > 1 ? smax / 64 : 1;
+  n = n < by_len ? n : by_len;
+  *num_splits = static_cast<int>(n < 1 ? 1 : n);
+  return LRI_OK;
 }
 
 extern "C" int lri_attn_decode(int dtype, const void* q, const void* k_cache, const void* v_cache,

@@ -245,11 +245,7 @@ int launch_hd(const ClusterDecodeParams& p, int B, int ns, cudaStream_t st) {
 }  // namespace
 
 bool attn_decode_cluster_supports(int num_splits) {
-  static const bool off = [] {
-    const char* e = getenv("LRI_ATTN_CLUSTER");
-    return e && e[0] == '0';
-  }();
-  return !off && (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8);
+  return option(OPT_ATTN_CLUSTER) != 0 && (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8);
 }
 
 int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, const void* v_cache,

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "lri_b200.h"
 
 namespace lri {
@@ -41,6 +43,51 @@ void count_launch(int n = 1);
   } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- tuning options ----------------------------------------------------------------------------
+// One table per process.  Every entry starts from its LRI_* environment variable (read once, at the
+// first use of any option) and can be changed at run time through lri_set_option(); the kernels'
+// launch code reads the table on every call, so a change takes effect on the next launch.
+enum Option {
+  OPT_STREAM_ROWS = 0,  // LRI_STREAM_ROWS    token rows up to which the weight-streaming kernels run (1..16, default 8)
+  OPT_GEMV_SIMT,        // LRI_GEMV_SMALL=simt  keep the SIMT streaming kernel for 2..8 rows (default 0)
+  OPT_GEMV_R,           // LRI_GEMV_R         weight rows per CTA of the SIMT streaming kernel: 2, 4 or 8 (0 = choose)
+  OPT_GEMV_U,           // LRI_GEMV_U         2 halves the loads in flight per thread of that kernel (0 = default)
+  OPT_GEMV_MT,          // LRI_GEMV_MT        row tiles per CTA of the tensor-core streaming kernel: 1, 2, 4 (0 = choose)
+  OPT_GEMM_GROUP,       // LRI_GEMM_GROUP     token tiles per panel of the prefill GEMM's tile walk (0 = choose)
+  OPT_FUSED_PREFILL,    // LRI_FUSED_PREFILL  0: prefill projections run the plain GEMM + an elementwise epilogue
+  OPT_PDL,              // LRI_PDL            0: no programmatic dependent launch
+  OPT_ATTN_CLUSTER,     // LRI_ATTN_CLUSTER   0: decode attention never takes the thread-block-cluster kernel
+  OPT_ATTN_MMA,         // LRI_ATTN_MMA       1 / 0 forces / forbids the tensor-core decode-attention kernel (-1 = choose)
+  OPT_DECODE_SPLITS,    // LRI_DECODE_SPLITS  fixed number of sequence ranges for decode attention (0 = choose)
+  OPT_FUSED_NORM,       // LRI_FUSED_NORM     1 / 0 forces / forbids add + RMSNorm inside the QKV and gate/up kernels (-1 = choose)
+  OPT_COUNT
+};
+int option(int which);
+
+// ---- per-device state -------------------------------------------------------------------------------
+// Function attributes (dynamic shared memory size) and the SM count belong to a device, not to the
+// process: one-time set-up is keyed by the ordinal of the device that is current at the call.
+int current_device();    // ordinal of the current device, -1 when the runtime cannot tell
+int device_sm_count();   // multiprocessors of the current device (148 when the runtime cannot tell)
+// LRI_ONCE_PER_DEVICE(seen, call): runs a CUDA runtime call the first time the enclosing launch code
+// is used on the current device (and again after a failure); `seen` is a static atomic bit set with one
+// bit per device ordinal.  Ordinals outside 0..63 repeat the call every time, which is harmless.
+inline bool device_setup_needed(const std::atomic<unsigned long long>& seen) {
+  const int dev = current_device();
+  return dev < 0 || dev >= 64 || (seen.load(std::memory_order_acquire) & (1ull << dev)) == 0;
+}
+inline void device_setup_done(std::atomic<unsigned long long>& seen) {
+  const int dev = current_device();
+  if (dev >= 0 && dev < 64) seen.fetch_or(1ull << dev, std::memory_order_release);
+}
+#define LRI_ONCE_PER_DEVICE(seen, call)      \
+  do {                                       \
+    if (::lri::device_setup_needed(seen)) {  \
+      LRI_CUDA(call);                        \
+      ::lri::device_setup_done(seen);        \
+    }                                        \
+  } while (0)
 
 // Programmatic dependent launch.  Kernels of the decode step are launched with the
 // programmatic-stream-serialization attribute: a kernel may start while its predecessor in the

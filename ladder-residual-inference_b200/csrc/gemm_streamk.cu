@@ -353,11 +353,8 @@ int launch(int dtype, const LinearParams& lin, float* partial, cudaStream_t st) 
   p.stages = stages > 8 ? 8 : stages;
   const int smem = p.stages * kStageBytes + 1024;
   auto kern = gemm_streamk_kernel<T, BN, EPI>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_set{0};  // per template instantiation, one bit per device
+  LRI_ONCE_PER_DEVICE(attr_set, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
   const int64_t ctas = plan_ctas(p.tiles, p.total_kt, p.max_seg);
   p.ctas = static_cast<int>(ctas);
   LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tw, tx,

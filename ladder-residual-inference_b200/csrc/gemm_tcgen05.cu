@@ -193,7 +193,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_con
       const WorkItem w = work_item(item, grid);
       const uint32_t a = it & 1;
       const uint32_t use = static_cast<uint32_t>(it) >> 1;
-      if (!mbar_wait(acc_full0 + 8 * a, use & 1u, &abort_flag, 3, &g_gemm_status)) break;
+      // the tcgen05.ld below is warp-collective: the warp leaves together or not at all
+      const bool ready = mbar_wait(acc_full0 + 8 * a, use & 1u, &abort_flag, 3, &g_gemm_status);
+      if (!__all_sync(0xffffffffu, ready)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kAccCols;
       if (!SWAP && EPI == EPI_SWIGLU) {
@@ -360,16 +362,7 @@ int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int64_t rows, int64_
   return LRI_OK;
 }
 
-int sm_count() {
-  static const int n = [] {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      v = 148;
-    return v;
-  }();
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 namespace {
 
@@ -390,21 +383,15 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
   stages = stages > 8 ? 8 : stages;
   const int smem = stages * kStageBytes + 1024;
   auto kern = gemm_tcgen05_kernel<T, BN, SWAP, EPI>;
-  static bool attr_set = false;  // per template instantiation
-  if (!attr_set) {
-    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_set{0};  // per template instantiation, one bit per device
+  LRI_ONCE_PER_DEVICE(attr_set, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024));
   const int64_t tiles_p = (p_rows + kBM - 1) / kBM;
   // SWIGLU: a Q tile is BN/2 outputs (their up rows and their gate rows)
   const int64_t tiles_q = EPI == EPI_SWIGLU ? (lin->n + BN / 2 - 1) / (BN / 2) : (q_rows + BN - 1) / BN;
   const int64_t items = tiles_p * tiles_q;
   if (items >= (1ll << 31)) return fail(LRI_ERR_UNSUPPORTED, "gemm: %lld output tiles", (long long)items);
   // panel of P tiles: about 16 MB of the P operand, between 4 and 16 tiles (LRI_GEMM_GROUP overrides)
-  static const int forced_group = [] {
-    const char* e = getenv("LRI_GEMM_GROUP");
-    return e ? atoi(e) : 0;
-  }();
+  const int forced_group = option(OPT_GEMM_GROUP);
   int64_t group = (16ll << 20) / (static_cast<int64_t>(kBM) * k * 2);
   group = group < 4 ? 4 : (group > 16 ? 16 : group);
   if (forced_group > 0) group = forced_group;

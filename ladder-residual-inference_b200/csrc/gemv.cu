@@ -8,6 +8,7 @@
 //   PLAIN   store (optionally + addend)                       wo / w2 / LM head
 //   SWIGLU  rows (j, I + j) -> silu(gate) * up                 w1
 //   QKV     rotate adjacent pairs, scatter q / k-cache / v-cache   wqkv
+//   ARGMAX  no logits stored: arg-max over rows and ranks           LM head, greedy decoding (argmax.cuh)
 #include <cstdlib>
 
 #include "linear.cuh"
@@ -109,6 +110,40 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
     }
   __syncthreads();
 
+  if (EPI == EPI_ARGMAX) {
+    // every thread stays: the CTA synchronises again before it takes its ticket
+    __shared__ unsigned long long best[M][R / 2];
+    if (threadIdx.x < M * (R / 2)) {
+      const int m = threadIdx.x / (R / 2), j = threadIdx.x % (R / 2);
+      float s0 = 0.f, s1 = 0.f;
+      for (int wi = 0; wi < W; ++wi) {
+        s0 += red[wi][m * R + 2 * j];
+        s1 += red[wi][m * R + 2 * j + 1];
+      }
+      // compare what the projection would have stored: logits rounded to the storage type
+      const int64_t n = static_cast<int64_t>(blockIdx.x) * R + 2 * j;
+      unsigned long long k = 0ull;
+      if (n < p.n) k = argmax_key(rnd<T>(s0), p.am.index_offset + n);
+      if (n + 1 < p.n) {
+        const unsigned long long k1 = argmax_key(rnd<T>(s1), p.am.index_offset + n + 1);
+        k = k1 > k ? k1 : k;
+      }
+      best[m][j] = k;
+    }
+    __syncthreads();
+    if (threadIdx.x < p.m) {
+      unsigned long long k = best[threadIdx.x][0];
+#pragma unroll
+      for (int j = 1; j < R / 2; ++j) k = best[threadIdx.x][j] > k ? best[threadIdx.x][j] : k;
+      argmax_offer(p.am, threadIdx.x, k);
+    }
+    __syncthreads();
+    __shared__ int last;
+    if (threadIdx.x == 0) last = argmax_last_cta(p.am, blockIdx.x, gridDim.x) ? 1 : 0;
+    __syncthreads();
+    if (last && warp == 0) argmax_finish(p.am);
+    return;
+  }
   if (threadIdx.x >= M * (R / 2)) return;
   const int m = threadIdx.x / (R / 2);
   const int j = threadIdx.x % (R / 2);
@@ -168,11 +203,7 @@ int launch_gemv(const LinearParams& p, cudaStream_t st) {
 // whatever R is; fewer rows per CTA mean more, shorter CTAs (less wave quantisation on small
 // projections), more rows mean fewer reductions.  LRI_GEMV_R=2|4|8 overrides the choice.
 int rows_per_cta(const LinearParams& p) {
-  static const int forced = [] {
-    const char* e = getenv("LRI_GEMV_R");
-    const int v = e ? atoi(e) : 0;
-    return (v == 2 || v == 4 || v == 8) ? v : 0;
-  }();
+  const int forced = option(OPT_GEMV_R);
   (void)p;
   return forced ? forced : 4;
 }
@@ -181,10 +212,7 @@ template <typename T, int EPI>
 int dispatch_m(const LinearParams& p, cudaStream_t st) {
   const int r = rows_per_cta(p);
   // LRI_GEMV_U=2: half the loads in flight per thread, fewer registers, more resident CTAs (tuning knob)
-  static const bool half_depth = [] {
-    const char* e = getenv("LRI_GEMV_U");
-    return e && atoi(e) == 2;
-  }();
+  const bool half_depth = option(OPT_GEMV_U) == 2;
   if (half_depth && p.m <= 1 && r == 4) return launch_gemv<T, 1, 4, 2, EPI>(p, st);
 #define LRI_GEMV_CASE(M_, U2, U4, U8)                                   \
   if (p.m <= M_) {                                                      \
@@ -205,6 +233,7 @@ int dispatch_epi(int epi, const LinearParams& p, cudaStream_t st) {
   switch (epi) {
     case EPI_PLAIN: return dispatch_m<T, EPI_PLAIN>(p, st);
     case EPI_SWIGLU: return dispatch_m<T, EPI_SWIGLU>(p, st);
+    case EPI_ARGMAX: return dispatch_m<T, EPI_ARGMAX>(p, st);
     default: return dispatch_m<T, EPI_QKV>(p, st);
   }
 }

@@ -204,11 +204,7 @@ int launch_mma(const LinearParams& p, cudaStream_t st) {
 // Row tiles per CTA: as many as still leave about two CTAs per SM (LRI_GEMV_MT=1|2|4 overrides).
 template <typename T, int NT, int EPI>
 int launch_tiles(const LinearParams& p, cudaStream_t st) {
-  static const int forced = [] {
-    const char* e = getenv("LRI_GEMV_MT");
-    const int v = e ? atoi(e) : 0;
-    return (v == 1 || v == 2 || v == 4) ? v : 0;
-  }();
+  const int forced = option(OPT_GEMV_MT);
   const int64_t tiles = (p.n + (EPI == EPI_SWIGLU ? 8 : 16) - 1) / (EPI == EPI_SWIGLU ? 8 : 16);
   int mt = tiles >= 4 * 296 ? 4 : (tiles >= 2 * 296 ? 2 : 1);
   if (forced) mt = forced;

@@ -1,11 +1,12 @@
 // Parameters and epilogue code shared by the GEMV (decode) and GEMM (prefill) linear kernels.
 #pragma once
 
+#include "argmax.cuh"
 #include "common.cuh"
 
 namespace lri {
 
-enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2 };
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_QKV = 2, EPI_ARGMAX = 3 };
 constexpr int kGemvMaxRows = 8;
 
 // Producer side of the split all-reduce, fused into the epilogue of a row-parallel projection:
@@ -37,6 +38,7 @@ struct LinearParams {
   int64_t smax, table_rows;
   int table_gathered;  // rope_table row s belongs to token s (rows already gathered by position)
   PushArgs push;       // PLAIN epilogue of the SIMT kernel only
+  ArgmaxArgs am;       // ARGMAX epilogue of the SIMT kernel: greedy choice instead of stored logits
 };
 
 // Epilogue of the QKV projection for token row `m` and the adjacent output pair (n, n+1),

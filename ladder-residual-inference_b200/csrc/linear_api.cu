@@ -18,10 +18,62 @@ int gemm_tcgen05_status_read_and_clear(int* status_out);
 bool gemm_tcgen05_fused_supports(int epi, const LinearParams& p, int64_t m);
 int gemm_tcgen05_fused_launch(int dtype, int epi, const LinearParams& p, int64_t m, cudaStream_t st);
 
-// ---- error text, launch counter, back-end switch ----------------------------------------------
+// ---- error text, launch counter, options --------------------------------------------------------
 namespace {
 thread_local char g_err[512] = "";
 std::atomic<int64_t> g_launches{0};
+
+struct OptionSpec {
+  const char* name;  // as given to lri_set_option / lri_get_option
+  const char* env;   // environment variable that supplies the initial value
+  int def, lo, hi;
+};
+// order = enum Option (common.cuh)
+const OptionSpec kOptionSpecs[OPT_COUNT] = {
+    {"stream_rows", "LRI_STREAM_ROWS", 8, 1, kGemvMmaMaxRows},
+    {"gemv_simt", "LRI_GEMV_SMALL", 0, 0, 1},
+    {"gemv_rows_per_cta", "LRI_GEMV_R", 0, 0, 8},
+    {"gemv_depth", "LRI_GEMV_U", 0, 0, 2},
+    {"gemv_mma_tiles", "LRI_GEMV_MT", 0, 0, 4},
+    {"gemm_group", "LRI_GEMM_GROUP", 0, 0, 1024},
+    {"fused_prefill", "LRI_FUSED_PREFILL", 1, 0, 1},
+    {"pdl", "LRI_PDL", 1, 0, 1},
+    {"attn_cluster", "LRI_ATTN_CLUSTER", 1, 0, 1},
+    {"attn_mma", "LRI_ATTN_MMA", -1, -1, 1},
+    {"decode_splits", "LRI_DECODE_SPLITS", 0, 0, 64},
+    {"fused_norm", "LRI_FUSED_NORM", -1, -1, 1},
+};
+
+bool option_value_ok(int which, int v) {
+  const OptionSpec& s = kOptionSpecs[which];
+  if (v < s.lo || v > s.hi) return false;
+  if (which == OPT_GEMV_R) return v == 0 || v == 2 || v == 4 || v == 8;
+  if (which == OPT_GEMV_U) return v == 0 || v == 2;
+  if (which == OPT_GEMV_MT) return v == 0 || v == 1 || v == 2 || v == 4;
+  return true;
+}
+
+struct OptionTable {
+  std::atomic<int> v[OPT_COUNT];
+  OptionTable() {
+    for (int i = 0; i < OPT_COUNT; ++i) {
+      int val = kOptionSpecs[i].def;
+      const char* e = getenv(kOptionSpecs[i].env);
+      if (e && *e) {
+        const int parsed = (i == OPT_GEMV_SIMT) ? (strcmp(e, "simt") == 0 ? 1 : 0) : atoi(e);
+        // out-of-range numbers are clamped (what the variables did before they became options)
+        int c = parsed < kOptionSpecs[i].lo ? kOptionSpecs[i].lo : (parsed > kOptionSpecs[i].hi ? kOptionSpecs[i].hi : parsed);
+        if (option_value_ok(i, c)) val = c;
+      }
+      v[i].store(val);
+    }
+  }
+};
+OptionTable& options() {
+  static OptionTable t;
+  return t;
+}
+
 // LRI_GEMM_BACKEND=simt|tcgen05 in the environment sets the initial choice (debugging aid).
 int backend_from_env() {
   const char* e = getenv("LRI_GEMM_BACKEND");
@@ -40,40 +92,40 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("LRI_PDL");
-    return !(e && strcmp(e, "0") == 0);
-  }();
-  return on;
+int option(int which) { return (which >= 0 && which < OPT_COUNT) ? options().v[which].load(std::memory_order_relaxed) : 0; }
+bool pdl_enabled() { return option(OPT_PDL) != 0; }
+
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return dev;
 }
+int device_sm_count() {
+  static std::atomic<int> cache[64];
+  const int dev = current_device();
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int v = 0;
+  if (dev < 0 || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  if (dev < 64) cache[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
 // Token rows up to which the weight-streaming kernels (no workspace) are used; more rows go to the
 // tcgen05 GEMM (measured cross-over on B200: the streaming kernels win up to 8 rows).
-// LRI_STREAM_ROWS=1..16 moves the limit (tuning knob).
-int streaming_rows() {
-  static const int rows = [] {
-    const char* e = getenv("LRI_STREAM_ROWS");
-    const int v = e ? atoi(e) : 8;
-    return v < 1 ? 1 : (v > kGemvMmaMaxRows ? kGemvMmaMaxRows : v);
-  }();
-  return rows;
-}
-// LRI_FUSED_PREFILL=0 keeps the prefill projections on the plain GEMM followed by an elementwise
+int streaming_rows() { return option(OPT_STREAM_ROWS); }
+// Option fused_prefill = 0 keeps the prefill projections on the plain GEMM followed by an elementwise
 // kernel (debugging aid; also what runs for shapes the fused epilogues do not take).
-bool fused_prefill_epilogues() {
-  static const bool on = [] {
-    const char* e = getenv("LRI_FUSED_PREFILL");
-    return !(e && strcmp(e, "0") == 0);
-  }();
-  return on;
-}
-bool prefer_simt_gemv() {
-  static const bool simt = [] {
-    const char* e = getenv("LRI_GEMV_SMALL");
-    return e && strcmp(e, "simt") == 0;
-  }();
-  return simt;
-}
+bool fused_prefill_epilogues() { return option(OPT_FUSED_PREFILL) != 0; }
+bool prefer_simt_gemv() { return option(OPT_GEMV_SIMT) != 0; }
 int current_gemm_backend() { return g_backend.load(); }
 
 namespace {
@@ -244,6 +296,26 @@ extern "C" int lri_set_gemm_backend(int backend) {
   LRI_REQUIRE(backend >= LRI_GEMM_AUTO && backend <= LRI_GEMM_SIMT, LRI_ERR_ARG, "set_gemm_backend: %d", backend);
   g_backend.store(backend);
   return LRI_OK;
+}
+extern "C" int lri_set_option(const char* name, int value) {
+  LRI_REQUIRE(name != nullptr, LRI_ERR_ARG, "set_option: NULL name");
+  for (int i = 0; i < OPT_COUNT; ++i)
+    if (strcmp(name, kOptionSpecs[i].name) == 0) {
+      LRI_REQUIRE(option_value_ok(i, value), LRI_ERR_ARG, "set_option: %s=%d is outside %d..%d (or not a value it takes)",
+                  name, value, kOptionSpecs[i].lo, kOptionSpecs[i].hi);
+      options().v[i].store(value);
+      return LRI_OK;
+    }
+  return fail(LRI_ERR_ARG, "set_option: unknown option '%s'", name);
+}
+extern "C" int lri_get_option(const char* name, int* value_out) {
+  LRI_REQUIRE(name != nullptr && value_out != nullptr, LRI_ERR_ARG, "get_option: NULL argument");
+  for (int i = 0; i < OPT_COUNT; ++i)
+    if (strcmp(name, kOptionSpecs[i].name) == 0) {
+      *value_out = option(i);
+      return LRI_OK;
+    }
+  return fail(LRI_ERR_ARG, "get_option: unknown option '%s'", name);
 }
 extern "C" int lri_gemm_status(void) {
   int v = 0, v2 = 0;

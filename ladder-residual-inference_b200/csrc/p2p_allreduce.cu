@@ -16,55 +16,11 @@
 #include <cstring>
 
 #include "linear.cuh"
+#include "p2p_comm.cuh"
 #include "p2p_ll.cuh"
-
-struct lri_comm {
-  int rank, world;
-  int64_t max_bytes;   // per slot
-  uint8_t* local;      // this rank's inbox (cudaMalloc)
-  uint8_t* peer[8];    // every rank's inbox as seen from this rank (peer[rank] == local)
-  size_t total_bytes;
-};
 
 namespace lri {
 namespace {
-
-constexpr int kMaxWorld = 8;
-constexpr int kMaxCtas = 64;
-constexpr int kArThreads = 256;
-
-struct Control {
-  unsigned int epoch;   // number of completed calls
-  unsigned int ticket;  // CTAs retired in the running call
-  int status;           // LRI_OK or LRI_ERR_TIMEOUT
-  int pad;
-  unsigned int chan_epoch[4];   // per push channel: number of messages consumed by this rank
-  unsigned int chan_ticket[4];  // per push channel: consumer CTAs that have finished reading
-};
-
-__host__ __device__ inline size_t data_bytes(int world, int64_t max_bytes) {
-  return static_cast<size_t>(2) * world * static_cast<size_t>(max_bytes);
-}
-__host__ __device__ inline size_t flags_offset(int world, int64_t max_bytes) { return data_bytes(world, max_bytes); }
-__host__ __device__ inline size_t control_offset(int world, int64_t max_bytes) {
-  return flags_offset(world, max_bytes) + static_cast<size_t>(2) * world * kMaxCtas * sizeof(unsigned int);
-}
-
-// Low-latency region: messages up to kLlMaxPayload bytes travel as 16-byte lines
-// {data, epoch, data, epoch}: every 8-byte half carries its own arrival flag, so the receiver
-// polls the data itself and neither a fence nor a separate flag store is on the critical path.
-constexpr int64_t kLlMaxPayload = 128 * 1024;
-constexpr int64_t kLlSlotBytes = 2 * kLlMaxPayload;
-__host__ __device__ inline size_t ll_offset(int world, int64_t max_bytes) {
-  return (control_offset(world, max_bytes) + 64 + 255) / 256 * 256;
-}
-__host__ __device__ inline size_t ll_bytes(int world) { return static_cast<size_t>(2) * world * kLlSlotBytes; }
-// Line regions: region 0 belongs to lri_allreduce, regions 1..kPushChannels to the push channels
-// (producer lri_comm_push, consumer lri_add_rmsnorm_gather), each with its own epoch counter.
-constexpr int kPushChannels = 2;
-__host__ __device__ inline size_t ll_region(int world, int64_t max_bytes, int region) {
-  return ll_offset(world, max_bytes) + static_cast<size_t>(region) * ll_bytes(world);
-}
 
 struct ArParams {
   uint8_t* inbox[kMaxWorld];
@@ -290,7 +246,7 @@ extern "C" int lri_comm_create(int rank, int world, int64_t max_elems, lri_comm*
   lri_comm* c = new lri_comm();
   c->rank = rank, c->world = world;
   c->max_bytes = ((max_elems * 2 + 255) / 256) * 256;
-  c->total_bytes = ll_region(world, c->max_bytes, 1 + kPushChannels);
+  c->total_bytes = ll_region(world, c->max_bytes, kLlRegions);
   for (int i = 0; i < 8; ++i) c->peer[i] = nullptr;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->local), c->total_bytes);
   if (e != cudaSuccess) {

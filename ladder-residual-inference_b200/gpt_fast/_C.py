@@ -28,6 +28,9 @@ _SIGNATURES = {
     "lri_set_gemm_backend": (c_int, [c_int]),
     "lri_launch_count": (c_int64, []),
     "lri_gemm_status": (c_int, []),
+    "lri_set_option": (c_int, [ctypes.c_char_p, c_int]),
+    "lri_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_int)]),
+    "lri_attn_decode_plan": (c_int, [c_int, c_int, c_int, c_int, c_int64, ctypes.POINTER(c_int)]),
     "lri_add_rmsnorm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p,
                                 c_int64, c_int, c_void_p]),
     "lri_embedding": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_void_p]),
@@ -61,6 +64,9 @@ _SIGNATURES = {
     "lri_comm_push": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "lri_add_rmsnorm_gather": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p,
                                        c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "lri_lm_head_argmax_scratch_bytes": (c_size_t, []),
+    "lri_lm_head_argmax": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
+                                   c_size_t, c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_void_p]),
     "lri_comm_status": (c_int, [c_void_p, c_void_p]),
     "lri_comm_destroy": (c_int, [c_void_p]),
 }

@@ -45,6 +45,21 @@ class NoComm:
         return None
 
 
+class ElidedComm(NoComm):
+    """The tensor-parallel group with every collective left out: same interface, all-reduces are
+    no-ops, so the engine launches exactly the kernels of a step minus the communication.  For
+    timing only (the step with communication minus this one is the exposed all-reduce time, the
+    reference's "upper bound" notion, gpt_fast/gpt_desync_TP.py:165-176); the logits are those of
+    unreduced partial sums."""
+    name = "elided"
+
+    def __init__(self, world, rank, like=None):
+        self.world, self.rank = world, rank
+        # the greedy head's (value, index) exchange is not an all-reduce and stays as it is
+        self.handle = getattr(like, "handle", None)
+        self.timeout_ms = getattr(like, "timeout_ms", 2000)
+
+
 class TorchComm:
     name = "torch.distributed"
 
@@ -191,7 +206,9 @@ class P2PComm:
                                              self.timeout_ms, torch.cuda.current_stream().cuda_stream))
 
     def status(self):
-        """Raises if a bounded peer wait gave up since the last check (synchronises the comm stream)."""
+        """Raises if a bounded peer wait gave up since the last check.  Waits for the compute stream
+        (gathering norms and in-stream all-reduces run there) and for the communication stream."""
+        torch.cuda.current_stream().synchronize()
         self._C.check(self._C.lib.lri_comm_status(self.handle, self.stream.cuda_stream))
 
     def close(self):

@@ -80,6 +80,13 @@ class Engine:
         self.vocab_hi = min(cfg.vocab_size, self.vocab_lo + self.vocab_per_rank)
         self.head_logits = torch.empty(max_batch * self.vocab_per_rank, dtype=dtype, device=device)
         self.head_best = torch.empty(t, max_batch, 2, dtype=torch.float32, device=device)
+        # fused greedy head (projection + arg-max over rows and ranks in one launch): needs peer memory
+        # for the exchange, i.e. one rank or the P2P communicator; NCCL-only groups use the torch ops below
+        self.head_tokens = torch.zeros(max_batch, dtype=torch.int32, device=device)
+        self.fused_head = hasattr(self.ops, "lm_head_argmax") and self.resid.is_cuda and max_batch <= 64 and \
+            (t == 1 or getattr(self.comm, "handle", None) is not None)
+        if self.fused_head:
+            self.head_scratch = torch.zeros(self.ops.lm_head_argmax_scratch_bytes(), dtype=torch.uint8, device=device)
         nbytes = self.ops.attn_decode_scratch_bytes(max_batch, self.nh, self.nkv, self.hd, _MAX_SPLITS)
         self.scratch = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
         # ladder decode runs the attention and MLP chains of a layer on two streams (LRI_LADDER_OVERLAP=0: one)
@@ -141,7 +148,7 @@ class Engine:
         if input_pos.dtype not in (torch.int32, torch.int64):
             input_pos = input_pos.to(torch.int64)
         rows = B * S
-        self._splits = decode_splits(B, self.nh, self.nkv, self.model.max_seq_length) if S == 1 else 1
+        self._splits = decode_splits(B, self.nh, self.nkv, self.model.max_seq_length, self.hd) if S == 1 else 1
         self.ops.embedding(self.model.tok_embeddings.weight, idx, self.resid)
         getattr(self, "_run_" + self.family)(rows, B, S, input_pos)
         return B, S, rows
@@ -154,21 +161,42 @@ class Engine:
         return logits
 
     @torch.no_grad()
+    def forward_last(self, idx, input_pos):
+        """Prompt pass that returns the logits of the last position only, [B, 1, V].  The reference
+        computes the output projection for every position (gpt_fast/gpt_ladder_TP.py:282-283) although
+        its generation loop reads only the last one (benchmark.py:82-83); for a long prompt that is
+        most of the LM-head work (32 x 4096 positions x 128256 logits = 33.6 GB of output)."""
+        B, S, rows = self._trunk(idx, input_pos)
+        last = self.normed[:rows].view(B, S, self.d)[:, -1].contiguous()
+        logits = torch.empty(B, 1, self.cfg.vocab_size, dtype=self.resid.dtype, device=self.resid.device)
+        self.ops.linear(last, self.model.output.weight, logits, B, workspace=self.ws_head)
+        return logits
+
+    @torch.no_grad()
     def forward_greedy(self, idx, input_pos):
         """Decode step that returns the arg-max token of every sequence, int32 [B, 1], instead of logits.
 
         The output projection is replicated on every rank (reference gpt_fast/gpt_ladder_TP.py:218, 283),
         and streaming all of it is the largest single item of a decode step at high TP.  Here rank r
         multiplies only rows [r V/t, (r+1) V/t) of its copy, takes the arg-max of its slice, and the
-        ranks exchange one (value, index) pair per sequence.  The logits of a row do not depend on
-        which other rows are computed, so the token is the one `forward(...).argmax(-1)` gives
-        (lowest index on ties), on every rank.
+        ranks exchange one (value, index) pair per sequence.  Up to 8 sequences the streaming kernels
+        compute every logit with a fixed K order whatever other rows are computed, so the token is
+        exactly the one `forward(...).argmax(-1)` gives (lowest index on ties), on every rank.  From 9
+        sequences on the stream-K kernel cuts K per tile by the number of tiles, which differs between
+        the full and the sliced head: logits agree to one rounding of the storage type and a near-tie
+        may resolve differently.
         """
         import torch.distributed as dist
         B, S, rows = self._trunk(idx, input_pos)
         assert S == 1, "forward_greedy is a decode step (one position per sequence)"
         n = self.vocab_hi - self.vocab_lo
         t = self.comm.world
+        if self.fused_head and (t == 1 or getattr(self.comm, "handle", None) is not None):
+            self.ops.lm_head_argmax(self.normed, self.model.output.weight[self.vocab_lo:self.vocab_hi], self.vocab_lo,
+                                    self.head_tokens, B, self.head_scratch, getattr(self.comm, "handle", None),
+                                    logits_ws=self.head_logits, workspace=self.ws_head,
+                                    timeout_ms=getattr(self.comm, "timeout_ms", 2000))
+            return self.head_tokens[:B].view(B, 1)
         mine = self.head_best[self.comm.rank, :B]
         if n > 0:
             local = self.head_logits[: B * n].view(B, n)

@@ -97,6 +97,12 @@ class TPModelBase(nn.Module):
         assert self.freqs_cis is not None, "Caches must be initialized first"
         return self._engine.forward(idx, input_pos)
 
+    def prefill_last(self, idx: Tensor, input_pos: Tensor) -> Tensor:
+        """forward(idx, input_pos)[:, -1:] without computing the other positions' logits (no
+        counterpart in the reference, whose forward always projects every position)."""
+        assert self.freqs_cis is not None, "Caches must be initialized first"
+        return self._engine.forward_last(idx, input_pos)
+
     def decode_greedy(self, idx: Tensor, input_pos: Tensor) -> Tensor:
         """Arg-max next token of every sequence, int32 [B, 1]; equal to
         `forward(idx, input_pos)[:, -1].argmax(-1)` but with the output projection split by

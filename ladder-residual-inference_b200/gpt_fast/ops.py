@@ -4,7 +4,7 @@
 tensors and raises otherwise.  The engine takes the ops object as a parameter so that host-side
 schedule logic can be exercised by tests with a stand-in.
 """
-import os
+import ctypes
 
 import torch
 
@@ -76,6 +76,27 @@ class CudaOps:
         _C.check(_C.lib.lri_gateup_swiglu(_C.dtype_code(x.dtype), x.data_ptr(), w1.data_ptr(), h.data_ptr(), rows,
                                           two_i // 2, k, ws_ptr, ws_bytes, _C.stream_handle()))
 
+    # ---- greedy head ---------------------------------------------------------------------------------
+    @staticmethod
+    def lm_head_argmax_scratch_bytes(rows=0, n=0):
+        return _C.lib.lri_lm_head_argmax_scratch_bytes()
+
+    @staticmethod
+    def lm_head_argmax(x, w, index_offset, token_out, rows, scratch, comm_handle=None, logits_ws=None, workspace=None,
+                       timeout_ms=2000):
+        """token_out[m] = arg-max over the whole vocabulary of sequence m, where `w` holds this rank's rows
+        starting at vocabulary index `index_offset` (w may have no rows)."""
+        _C.require_cuda(x, token_out, scratch)
+        assert token_out.dtype == torch.int32
+        n = w.shape[0]
+        k = w.shape[1] if w.dim() == 2 else x.shape[-1]
+        lw_ptr, lw_bytes = (logits_ws.data_ptr(), logits_ws.numel() * logits_ws.element_size()) if logits_ws is not None else (None, 0)
+        ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
+        _C.check(_C.lib.lri_lm_head_argmax(comm_handle, _C.dtype_code(x.dtype), x.data_ptr(), w.data_ptr() if n else None,
+                                           rows, n, k, index_offset, token_out.data_ptr(), scratch.data_ptr(),
+                                           scratch.numel() * scratch.element_size(), lw_ptr, lw_bytes, ws_ptr, ws_bytes,
+                                           timeout_ms, _C.stream_handle()))
+
     # ---- attention ---------------------------------------------------------------------------------
     @staticmethod
     def attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits):
@@ -98,29 +119,10 @@ class CudaOps:
                                              smax, _C.stream_handle()))
 
 
-def decode_splits(B, n_head, n_kv, smax, sm_count=148, head_dim=128):
+def decode_splits(B, n_head, n_kv, smax, head_dim=128):
     """Number of sequence ranges for decode attention, fixed per cache geometry so that the launch
-    grid never depends on the current position.  Up to 8 ranges (a power of two) run as one
-    thread-block cluster and merge through shared memory; that form is kept as long as a CTA
-    then streams at most ~1 MB of K/V.  Longer caches take more ranges (up to 64, at least 64
-    positions each) and merge through the scratch buffer."""
-    forced = os.environ.get("LRI_DECODE_SPLITS")  # tuning knob
-    if forced:
-        return max(1, min(64, int(forced), max(1, smax // 32)))
-    g = n_head // n_kv
-    mma = os.environ.get("LRI_ATTN_MMA")
-    if g <= 16 and (mma == "1" or (mma is None and B * n_kv >= 128)):
-        # tensor-core kernel (one CTA per sequence, KV head and range; two CTAs per SM): a second
-        # range only while one range per pair would leave SMs without work; more ranges cost more
-        # in the merge than they gain
-        return 2 if (B * n_kv < 2 * sm_count and smax >= 256) else 1
-    gt = 4 if g % 4 == 0 else (2 if g % 2 == 0 else 1)
-    base = max(1, B * n_kv * (g // gt))
-    want = max(1, -(-2 * sm_count // base))
-    bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8
-    if want <= 8 or bytes_per_cta_at_8 <= (1 << 20):
-        n = 1
-        while n * 2 <= min(want, 8) and smax // (n * 2) >= 32:
-            n *= 2
-        return n
-    return int(max(1, min(want, 64, max(1, smax // 64))))
+    grid never depends on the current position.  The rule lives in the library
+    (lri_attn_decode_plan), next to the choice of the kernel it has to agree with."""
+    n = ctypes.c_int(0)
+    _C.check(_C.lib.lri_attn_decode_plan(B, n_head, n_kv, head_dim, smax, ctypes.byref(n)))
+    return n.value

@@ -144,7 +144,7 @@ def _attention_core(mod, q, input_pos, bsz, seqlen):
     y = torch.empty(bsz * seqlen, mod.n_head * mod.head_dim, dtype=q.dtype, device=q.device)
     scratch, splits = None, 1
     if seqlen == 1:
-        splits = decode_splits(bsz, mod.n_head, mod.n_local_heads, kc.shape[2])
+        splits = decode_splits(bsz, mod.n_head, mod.n_local_heads, kc.shape[2], mod.head_dim)
         nbytes = ops.attn_decode_scratch_bytes(bsz, mod.n_head, mod.n_local_heads, mod.head_dim, splits)
         scratch = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
     ops.attention(q, kc, vc, input_pos, y, bsz, seqlen, mod.n_head, mod.n_local_heads, mod.head_dim, scratch, splits)

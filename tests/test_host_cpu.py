@@ -91,13 +91,14 @@ def test_workspace_sizes():
     assert rc == -1
 
 
-def test_decode_splits_choice(monkeypatch):
+def test_decode_splits_choice():
     """Number of position ranges of decode attention: fixed per cache geometry (never a function of
     the current position), a power of two up to 8 for the cluster kernel, up to 64 ranges of at
     least 64 positions for long caches, and one or two ranges once the tensor-core kernel takes over."""
+    from gpt_fast import _C
     from gpt_fast.ops import decode_splits
-    monkeypatch.delenv("LRI_ATTN_MMA", raising=False)
-    monkeypatch.delenv("LRI_DECODE_SPLITS", raising=False)
+    _C.check(_C.lib.lri_set_option(b"attn_mma", -1))
+    _C.check(_C.lib.lri_set_option(b"decode_splits", 0))
     for B in (1, 2, 4, 8):
         for nh, nkv in ((32, 8), (64, 8), (8, 1), (4, 4)):
             for smax in (64, 256, 1288, 8192, 131072):
@@ -108,10 +109,31 @@ def test_decode_splits_choice(monkeypatch):
     assert decode_splits(16, 32, 8, 1288) == 2          # 128 (sequence, KV head) pairs: tensor-core kernel, two ranges
     assert decode_splits(64, 32, 8, 1288) == 1          # 512 pairs: one range each
     assert decode_splits(64, 4, 1, 1288) == 4           # TP=8 shard: below 128 pairs, the cluster kernel
-    monkeypatch.setenv("LRI_ATTN_MMA", "0")
-    assert decode_splits(64, 32, 8, 1288) == 1 and decode_splits(16, 32, 8, 1288) == 2   # the cluster kernel's own choice
-    monkeypatch.setenv("LRI_DECODE_SPLITS", "5")
-    assert decode_splits(3, 32, 8, 1288) == 5
+    try:
+        _C.check(_C.lib.lri_set_option(b"attn_mma", 0))
+        assert decode_splits(64, 32, 8, 1288) == 1 and decode_splits(16, 32, 8, 1288) == 2   # the cluster kernel's own choice
+        _C.check(_C.lib.lri_set_option(b"decode_splits", 5))
+        assert decode_splits(3, 32, 8, 1288) == 5
+    finally:
+        _C.check(_C.lib.lri_set_option(b"attn_mma", -1))
+        _C.check(_C.lib.lri_set_option(b"decode_splits", 0))
+
+
+def test_options_table():
+    """Tuning options are one table behind the C ABI: readable, settable, range-checked."""
+    import ctypes
+    from gpt_fast import _C
+    v = ctypes.c_int(-99)
+    _C.check(_C.lib.lri_get_option(b"stream_rows", ctypes.byref(v)))
+    assert v.value == 8
+    assert _C.lib.lri_set_option(b"stream_rows", 17) == -1 and _C.lib.lri_set_option(b"no_such_option", 1) == -1
+    assert _C.lib.lri_set_option(b"gemv_rows_per_cta", 3) == -1
+    _C.check(_C.lib.lri_set_option(b"stream_rows", 4))
+    _C.check(_C.lib.lri_get_option(b"stream_rows", ctypes.byref(v)))
+    assert v.value == 4
+    assert _C.lib.lri_linear_workspace_bytes(8, 4096) > 0   # 8 rows now belong to the stream-K kernel
+    _C.check(_C.lib.lri_set_option(b"stream_rows", 8))
+    assert _C.lib.lri_linear_workspace_bytes(8, 4096) == 0
 
 
 def test_bench_roofline_arithmetic():

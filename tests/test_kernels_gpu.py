@@ -280,3 +280,61 @@ def test_argument_errors_are_reported():
                                        1, 4, 2, 48, 16, None))
     with pytest.raises(TypeError):
         c.dtype_code(torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 256), (1, 16032, 4096), (2, 4104, 512), (5, 777 * 8, 1024), (8, 2048, 2048),
+                                   (9, 4096, 512), (16, 16032, 1024), (33, 520, 256)])
+def test_lm_head_argmax_single_rank(dtype, M, N, K):
+    """Projection + arg-max in one launch (M <= 8) or projection, then fold (M > 8), against the
+    arg-max of the oracle's rounded logits; two calls in a row on one scratch buffer (each call must
+    leave the keys and tickets at zero); an index offset; duplicated rows to force exact ties, which
+    must resolve to the lowest index."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = _randn(g, M, K, dtype=dtype)
+    w = _randn(g, N, K, scale=0.05, dtype=dtype)
+    ops = _ops()
+    scratch = torch.zeros(ops.lm_head_argmax_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    logits_ws = torch.empty(M * N, dtype=dtype, device="cuda")
+    nbytes = ops.linear_workspace_bytes(M, N)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda") if nbytes else None
+    for rep, offset in enumerate((0, 4096)):
+        if rep == 1:
+            # copy the winning row of every sequence to a later and an earlier position: exact ties
+            ref = lo.linear(x, w).float()
+            for m in range(M):
+                win = ref[m].argmax().item()
+                w[(win + 17) % N] = w[win]
+                w[(win * 3 + 5) % N] = w[win]
+        ref = lo.linear(x, w).float()   # rounded to the storage type, as the projection stores them
+        want = ref.argmax(-1)
+        # lowest index among exact ties
+        want = torch.tensor([int((ref[m] == ref[m].max()).nonzero()[0]) for m in range(M)])
+        tok = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+        ops.lm_head_argmax(x.cuda(), w.cuda(), offset, tok, M, scratch, None, logits_ws=logits_ws, workspace=ws)
+        got = tok.cpu().long() - offset
+        for m in range(M):
+            if got[m] != want[m]:
+                # a different summation order may move a logit by one rounding step: accept another row
+                # only if its oracle logit is within one unit in the last place of the maximum
+                eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+                assert 0 <= got[m] < N and ref[m, got[m]] >= ref[m].max() - 2 * eps * ref[m].max().abs(), \
+                    f"rep {rep} row {m}: token {got[m].item()} (logit {ref[m, got[m]].item()}) vs {want[m].item()} ({ref[m].max().item()})"
+    assert int(scratch.view(torch.int32).abs().sum().item()) == 0
+
+
+def test_lm_head_argmax_empty_slice_and_errors():
+    ops = _ops()
+    c = _C()
+    x = torch.randn(2, 64).to(torch.bfloat16).cuda()
+    scratch = torch.zeros(ops.lm_head_argmax_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    tok = torch.full((2,), 7, dtype=torch.int32, device="cuda")
+    w = torch.empty(0, 64, dtype=torch.bfloat16, device="cuda")
+    ops.lm_head_argmax(x, w, 0, tok, 2, scratch)     # a rank without rows still takes part; one rank: key 0
+    torch.cuda.synchronize()
+    assert int(scratch.view(torch.int32).abs().sum().item()) == 0
+    small = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    w2 = torch.randn(8, 64).to(torch.bfloat16).cuda()
+    rc = c.lib.lri_lm_head_argmax(None, c.BF16, x.data_ptr(), w2.data_ptr(), 2, 8, 64, 0, tok.data_ptr(), small.data_ptr(),
+                                  64, None, 0, None, 0, 100, None)
+    assert rc == -5

@@ -182,9 +182,12 @@ def test_decode_greedy_and_decode_sample_match_the_rule_on_the_logits(family):
 
 
 @pytest.mark.parametrize("head", ["replicated", "vocab-parallel"])
-def test_device_loop_matches_step_by_step_greedy(head):
+def test_device_loop_matches_oracle_greedy_generate(head):
     """generate.DeviceLoop (several decode steps per graph replay, token feedback and position on the
-    device) must produce the tokens of a host-driven greedy loop."""
+    device) against the oracle's greedy generation (benchmark.py:118-164 with top_k = 1).  Free-running
+    generations may part ways at a near-tie, so a token may differ only where the oracle's own
+    top-1 margin at that step is inside the numeric tolerance; up to there the tokens must be equal,
+    and the test requires most of the sequence to be decided that way."""
     from gpt_fast.generate import DeviceLoop
     gold = gu.load(1)
     family, key = "ladder", "ladder-bfloat16-tp1-loud"
@@ -193,25 +196,27 @@ def test_device_loop_matches_step_by_step_greedy(head):
     n_new = 7
     prompt = torch.from_numpy(gold[key + "/prompt"])
     x = prompt.view(1, -1).repeat(gu.BATCH, 1).cuda()
+    oracle = lo.OracleModel(family, cfg, full, 1, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1)
+    want, step_logits = lo.greedy_generate(oracle, prompt, gu.BATCH, n_new + 1)   # [B, n_new + 1], first = prompt pass
 
-    def prefill(model):
-        with torch.no_grad():
-            return model(x, torch.arange(gu.PROMPT, device="cuda"))[:, -1].argmax(-1, keepdim=True).to(torch.int32)
-
-    model = build_model(family, cfg, full, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1)
-    first = prefill(model)
-    want, tok = [], first
+    model = build_model(family, cfg, full, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1, name="test-preset-loop")
     with torch.no_grad():
-        for n in range(n_new):
-            tok = model(tok, torch.tensor([gu.PROMPT + n], dtype=torch.int32, device="cuda"))[:, -1].argmax(-1, keepdim=True)
-            want.append(tok.to(torch.int32))
-    want = torch.cat(want, dim=1).cpu()
-
-    model2 = build_model(family, cfg, full, torch.bfloat16, gu.BATCH, gu.PROMPT + n_new + 1, name="test-preset-loop")
-    loop = DeviceLoop(model2, gu.BATCH, steps_per_replay=4, head=head)
-    loop.start(prefill(model2), gu.PROMPT)
-    got = loop.run(n_new).cpu()
-    assert torch.equal(got, want), f"{got.tolist()} vs {want.tolist()}"
+        first = model(x, torch.arange(gu.PROMPT, device="cuda"))[:, -1].argmax(-1, keepdim=True).to(torch.int32)
+    loop = DeviceLoop(model, gu.BATCH, steps_per_replay=4, head=head)
+    loop.start(first, gu.PROMPT)
+    got = torch.cat([first, loop.run(n_new)], dim=1).cpu().long()
+    equal_steps = 0
+    for b in range(gu.BATCH):
+        for n in range(n_new + 1):
+            if got[b, n] == want[b, n]:
+                equal_steps += 1
+                continue
+            lg = step_logits[n][b].float()
+            top2 = lg.topk(2).values
+            assert (top2[0] - top2[1]).item() <= 2e-2 * lg.abs().max().item(), \
+                f"row {b} step {n}: {got[b].tolist()} vs oracle {want[b].tolist()} at a decided step"
+            break  # the sequences legitimately differ from here on
+    assert equal_steps >= 0.75 * gu.BATCH * (n_new + 1), f"{got.tolist()} vs {want.tolist()}"
 
 
 def test_module_level_forward_matches_engine():

@@ -17,13 +17,20 @@ def test_model_matches_reference(family, dtype_name, tp, init):
     model = lo.OracleModel(family, cfg, full, tp, dtype, gu.BATCH, gu.PROMPT + gu.NEW)
     steps, prefill_row0 = gu.replay(model.forward, gold, key)
     ref = torch.from_numpy(gold[key + "/logits"])
-    # fp32: only summation order differs.  bf16: same rounding points, but the reference's
-    # matmul/SDPA kernels accumulate in another order and its all-reduce rounds per hop.
-    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    # fp32: only summation order differs (observed <= 1.2e-6).  bf16: same rounding points, but the
+    # reference's matmul/SDPA kernels accumulate in another order and its all-reduce rounds per hop
+    # (observed: 1.41e-2 under the loud init, whose activations are 10x larger, 2.4e-3 under the
+    # benchmark's quiet init).  Bounds = observed + margin for another host's BLAS summation order.
+    tol = 5e-6 if dtype == torch.float32 else (1.8e-2 if init == "loud" else 5e-3)
     assert gu.rel_err(steps, ref) < tol
     assert gu.rel_err(prefill_row0, gold[key + "/prefill_row0"]) < tol
-    agree = (steps.argmax(-1) == ref.argmax(-1)).float().mean().item()
-    assert agree >= (1.0 if dtype == torch.float32 else 0.8)
+    # top-1: every row whose reference margin (top-1 minus top-2) exceeds the tolerance must agree
+    # (observed: all rows agree in all 16 cases)
+    top2 = ref.topk(2, dim=-1).values
+    decided = (top2[..., 0] - top2[..., 1]) > tol * ref.abs().amax(dim=-1)
+    same = steps.argmax(-1) == ref.argmax(-1)
+    assert bool(same[decided].all())
+    assert same.float().mean().item() >= (1.0 if dtype == torch.float32 else 0.95)
 
 
 def test_schedules_are_told_apart_by_loud_init():

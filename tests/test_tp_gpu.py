@@ -1,6 +1,7 @@
-"""Tensor-parallel tests on 2 GPUs (skipped on a single-GPU box): the one-shot peer all-reduce,
-whole-model parity at TP = 2 against the reference's fixtures under both communication back ends,
-graph capture with the communication stream, and the bounded wait of the all-reduce."""
+"""Tensor-parallel tests on 2, 4 and 8 GPUs (each skipped when the box has fewer): the one-shot peer
+all-reduce, whole-model parity of an 8-KV-head model against the oracle at the same number of ranks
+and against the one-rank oracle, rank agreement, both communication back ends, graph capture with the
+communication stream; at 2 ranks also the reference's TP = 2 fixtures and the bounded wait."""
 import os
 import subprocess
 import sys
@@ -12,13 +13,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_worker():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29811", os.path.join(ROOT, "tests", "tp_gpu_worker.py")]
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_worker(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29811 + world), os.path.join(ROOT, "tests", "tp_gpu_worker.py")]
     # NVLS off: a rank that leaves while its memory is bound to an NVLink switch-reduction object can fault its peers
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=1200, env=env)
     sys.stdout.write(r.stdout[-4000:])
     assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
-    assert "TP-GPU-OK" in r.stdout
+    assert f"TP-GPU-OK world={world}" in r.stdout

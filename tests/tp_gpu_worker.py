@@ -1,4 +1,12 @@
-"""One rank of the 2-GPU tensor-parallel test (started by tests/test_tp_gpu.py via torch.distributed.run)."""
+"""One rank of the multi-GPU tensor-parallel test (started by tests/test_tp_gpu.py via
+torch.distributed.run with 2, 4 or 8 ranks).
+
+At every world size: the peer all-reduce against a rank-ordered fp32 sum, a model with 8 KV heads
+(so that it shards 8 ways) under the ladder / dense / parallel / desync schedules against the CPU
+oracle simulating the same number of ranks, tensor-parallel invariance against the one-rank oracle,
+bit-equality of the ranks' logits, both communication back ends, the split (push + gather) form of
+the all-reduce, graph capture with the communication stream, the vocabulary-parallel greedy head.
+At 2 ranks also the fixtures the reference itself produced at TP = 2, and the bounded wait."""
 import ctypes
 import os
 import sys
@@ -19,6 +27,13 @@ from oracle import ladder_oracle as lo  # noqa: E402
 
 rank, world = dist.get_rank(), dist.get_world_size()
 dev = torch.device("cuda", torch.cuda.current_device())
+torch.set_num_threads(2)  # every rank runs the CPU oracle; keep the host usable with 8 of them
+
+# 8 KV heads: shards over 2, 4 and 8 ranks (one KV head per rank at 8)
+WIDE = dict(block_size=256, vocab_size=2048, n_layer=3, n_head=16, n_local_heads=8, dim=1024, intermediate_size=2048,
+            rope_base=500000)
+WIDE_DESYNC = [{"attention": False, "mlp": True}, {"attention": True, "mlp": False}, {"attention": False, "mlp": False}]
+WIDE_B, WIDE_T, WIDE_NEW = 2, 40, 5
 
 
 def log(*a):
@@ -46,7 +61,7 @@ def check_p2p_allreduce():
     return c
 
 
-def build(family, cfg, full, dtype, name):
+def build(family, cfg, full, dtype, name, batch=gu.BATCH, max_seq=gu.PROMPT + gu.NEW):
     mods = {"ladder": (gpt_ladder_TP, gpt_fast.GPTLadder), "dense": (gpt_dense_TP, gpt_fast.GPTDense),
             "parallel": (gpt_parallel_TP, gpt_fast.GPTParallel), "desync": (gpt_desync_TP, gpt_fast.GPTDesync)}
     mod, cls = mods[family]
@@ -58,8 +73,113 @@ def build(family, cfg, full, dtype, name):
         model = cls.from_name(name)
     model = model.to(dtype=dtype).to_empty(device=dev).eval()
     gu.load_shards(model, family, cfg, full, rank, world, dtype)
-    model.setup_caches(max_batch_size=gu.BATCH, max_seq_length=gu.PROMPT + gu.NEW)
+    model.setup_caches(max_batch_size=batch, max_seq_length=max_seq)
     return model
+
+
+def wide_config(family):
+    return lo.OracleConfig(**WIDE, reduce_pattern=WIDE_DESYNC if family == "desync" else None)
+
+
+def ranks_agree(t, what):
+    """Every rank holds bit-identical values (the all-reduces sum in a fixed order)."""
+    t = t.contiguous()
+    mine = t.view(torch.int16) if t.element_size() == 2 else t
+    lo_, hi_ = mine.clone(), mine.clone()
+    dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+    assert torch.equal(lo_, hi_), f"{what}: ranks disagree"
+
+
+def check_wide_models(comm_name, split):
+    """The 8-KV-head model at this world size: prompt pass of 2 x 40 tokens (80 rows: tcgen05 GEMMs, a
+    160 KB all-reduce) and teacher-forced decode steps at batch 2 and batch 1, against the oracle that
+    simulates `world` ranks, against the one-rank oracle (tensor-parallel invariance), and across ranks."""
+    os.environ["LRI_COMM"] = comm_name
+    os.environ["LRI_SPLIT_AR"] = "1" if split else "0"
+    comm_mod.reset_comm()
+    for family in gu.FAMILIES:
+        cfg = wide_config(family)
+        full = lo.make_full_weights(cfg, 909, std=0.05, norm_mean=1.0, norm_std=0.1)
+        for B in (WIDE_B, 1):
+            model = build(family, cfg, full, torch.bfloat16, "wide-tp", batch=B, max_seq=WIDE_T + WIDE_NEW)
+            assert model._engine.comm.name == ("p2p-oneshot" if comm_name == "p2p" else "torch.distributed")
+            oracle = lo.OracleModel(family, cfg, full, world, torch.bfloat16, B, WIDE_T + WIDE_NEW)
+            single = lo.OracleModel(family, cfg, full, 1, torch.bfloat16, B, WIDE_T + WIDE_NEW) if family != "desync" else None
+            g = torch.Generator().manual_seed(31)
+            x = torch.randint(0, cfg.vocab_size, (WIDE_T,), generator=g).view(1, -1).repeat(B, 1)
+            idx, pos = x, torch.arange(WIDE_T)
+            for n in range(WIDE_NEW):
+                with torch.no_grad():
+                    logits = model(idx.to(dev), pos.to(dev))
+                got = logits.float().cpu()
+                ref = oracle.forward(idx, pos).float()
+                what = f"{comm_name} split={split} {family} B={B} world={world} step {n}"
+                if family != "desync":
+                    ranks_agree(logits, what)
+                    one = single.forward(idx, pos).float()
+                    e1 = gu.rel_err(got[:, -1], one[:, -1])
+                    assert e1 < 2e-2, f"{what}: {e1:.3e} from the one-rank oracle"
+                if family != "desync" or rank == 0:
+                    err = gu.rel_err(got[:, -1], ref[:, -1])
+                    assert err < 2e-2, f"{what}: rel err {err:.3e}"
+                    if n == 0:
+                        assert gu.rel_err(got, ref) < 2e-2, f"{what}: prompt pass, all positions"
+                if family != "desync" and n == WIDE_NEW - 1:
+                    with torch.no_grad():
+                        tok = model.decode_greedy(idx.to(dev), pos.to(dev))
+                    ranks_agree(tok, what + " greedy")
+                    want = got[:, -1].argmax(-1).to(torch.int32).view(-1, 1)
+                    assert torch.equal(tok.cpu(), want), f"{what}: greedy {tok.flatten().tolist()} vs {want.flatten().tolist()}"
+                idx = ref[:, -1].argmax(-1, keepdim=True)  # teacher forcing with the oracle's token
+                pos = torch.tensor([WIDE_T + n], dtype=torch.int32)
+            model._engine.comm.status()
+    os.environ["LRI_SPLIT_AR"] = "1"
+    log(f"8-KV-head model ok at world={world} with comm={comm_name} split={split}")
+
+
+def check_wide_graph():
+    """A captured ladder decode step (two compute streams + the communication stream) replayed with the
+    position advanced in place, at this world size, against the oracle."""
+    os.environ["LRI_COMM"] = "p2p"
+    os.environ["LRI_SPLIT_AR"] = "auto"
+    comm_mod.reset_comm()
+    cfg = wide_config("ladder")
+    full = lo.make_full_weights(cfg, 909, std=0.05, norm_mean=1.0, norm_std=0.1)
+    B = 1
+    model = build("ladder", cfg, full, torch.bfloat16, "wide-tp", batch=B, max_seq=WIDE_T + 8)
+    oracle = lo.OracleModel("ladder", cfg, full, world, torch.bfloat16, B, WIDE_T + 8)
+    g = torch.Generator().manual_seed(32)
+    x = torch.randint(0, cfg.vocab_size, (B, WIDE_T), generator=g)
+    ref = oracle.forward(x, torch.arange(WIDE_T)).float()
+    with torch.no_grad():
+        model(x.to(dev), torch.arange(WIDE_T, device=dev))
+        tok = ref[:, -1].argmax(-1, keepdim=True).to(torch.int32).to(dev)
+        pos = torch.tensor([WIDE_T], dtype=torch.int32, device=dev)
+        cache0 = [(l.attention.kv_cache.k_cache.clone(), l.attention.kv_cache.v_cache.clone()) for l in model.layers]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model(tok, pos)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = model(tok, pos)
+        for n in range(6):
+            pos.fill_(WIDE_T + n)
+            graph.replay()
+            torch.cuda.synchronize()
+            r = oracle.forward(tok.cpu().long(), torch.tensor([WIDE_T + n])).float()
+            err = gu.rel_err(logits[:, -1].float().cpu(), r[:, -1])
+            assert err < 2e-2, f"graph replay {n} at world={world}: {err:.3e}"
+            ranks_agree(logits, f"graph replay {n}")
+            tok.copy_(r[:, -1].argmax(-1, keepdim=True).to(torch.int32))
+    model._engine.comm.status()
+    del cache0
+    log(f"graph capture with the communication stream ok at world={world}")
 
 
 def check_models(comm_name, split=True):
@@ -214,14 +334,19 @@ def check_bounded_wait():
 def main():
     c = check_p2p_allreduce()
     c.close()
-    check_models("nccl")
-    check_models("p2p", split=True)    # push after the projection, reduction inside the next add + norm
-    check_models("p2p", split=False)   # stand-alone all-reduce kernel
-    check_split_single_row()
-    check_graph_with_comm()
-    check_bounded_wait()
+    check_wide_models("nccl", split=False)
+    check_wide_models("p2p", split=True)    # push after the projection, reduction inside the next add + norm
+    check_wide_models("p2p", split=False)   # stand-alone all-reduce kernel
+    check_wide_graph()
+    if world == 2:  # the reference's own TP = 2 fixtures (a 2-KV-head model) and the two-rank timeout scenario
+        check_models("nccl")
+        check_models("p2p", split=True)
+        check_models("p2p", split=False)
+        check_split_single_row()
+        check_graph_with_comm()
+        check_bounded_wait()
     dist.barrier()
-    log("TP-GPU-OK")
+    log(f"TP-GPU-OK world={world}")
 
 
 if __name__ == "__main__":
