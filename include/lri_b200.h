@@ -148,7 +148,7 @@ int lri_gateup_swiglu(int dtype, const void* x, const void* w1, void* h, int64_t
  * lri_attn_decode_scratch_bytes(B, n_head, n_kv, head_dim, num_splits) bytes, 16-byte aligned;
  * its first 32768 bytes are arrival counters that must be zero before the first call
  * (each call leaves them zero).  Calls sharing one scratch must not overlap on the device.
- * Three kernels serve this entry point: with 1, 2, 4 or 8 ranges and fewer than 128 (sequence,
+ * Three kernels serve this entry point: with 1, 2, 4, 8 or 16 ranges and fewer than 128 (sequence,
  * KV head) pairs the ranges are the CTAs of one thread-block cluster and merge through
  * distributed shared memory (scratch untouched); from 128 pairs on (and n_head / n_kv <= 16) a
  * tensor-core kernel takes the query heads of a KV head as the rows of mma tiles and merges the

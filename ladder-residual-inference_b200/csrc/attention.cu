@@ -13,6 +13,11 @@ bool attn_decode_cluster_supports(int num_splits);
 int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, const void* v_cache,
                                const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
                                int head_dim, int64_t smax, int num_splits, float scale_log2, cudaStream_t st);
+// tcgen05 / TMEM form of the prefill kernel (attention_tc.cu)
+bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, int64_t smax);
+int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
+                           int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
+                           float scale_log2, int variant, cudaStream_t st);
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -856,8 +861,8 @@ extern "C" size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int
 }
 
 // Number of sequence ranges, fixed per cache geometry so that the launch grid never depends on the
-// current position.  Up to 8 ranges (a power of two) run as one thread-block cluster and merge
-// through shared memory; that form is kept as long as a CTA then streams at most ~1 MB of K/V.
+// current position.  Up to 16 ranges (a power of two; 16 only while there are at most 8 clusters) run
+// as one thread-block cluster and merge through shared memory; that form is kept as long as a CTA then streams at most ~1 MB of K/V.
 // Longer caches take more ranges (up to 64, at least 64 positions each) and merge through the scratch
 // buffer.  The tensor-core kernel (from 128 (sequence, KV head) pairs on) takes one range per pair,
 // two only while one per pair would leave SMs without work.
@@ -882,8 +887,10 @@ extern "C" int lri_attn_decode_plan(int B, int n_head, int n_kv, int head_dim, i
   const int64_t want = (2 * sms + base - 1) / base;
   const int64_t bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8;
   if (want <= 8 || bytes_per_cta_at_8 <= (1 << 20)) {
+    // a cluster of 16 (the hardware's opt-in maximum) while at most 8 clusters are launched: one per GPC
+    const int64_t cap = (base <= 8 && attn_decode_cluster_supports(16)) ? 16 : 8;
     int n = 1;
-    const int64_t lim = want < 8 ? want : 8;
+    const int64_t lim = want < cap ? want : cap;
     while (n * 2 <= lim && smax / (n * 2) >= 32) n *= 2;
     *num_splits = n;
     return LRI_OK;
@@ -908,7 +915,7 @@ extern "C" int lri_attn_decode(int dtype, const void* q, const void* k_cache, co
               "attn_decode: pointers must be 16-byte aligned");
   const bool mma = attn_mma_wanted(B, n_kv) && n_head / n_kv <= kMmaDecMaxGroup && scratch != nullptr;
   if (!mma && attn_decode_cluster_supports(num_splits)) {
-    // 1, 2, 4 or 8 splits: the splits are the CTAs of one cluster and merge through distributed
+    // 1, 2, 4, 8 or 16 splits: the splits are the CTAs of one cluster and merge through distributed
     // shared memory; the scratch buffer is not touched
     if (B == 0) return LRI_OK;
     return attn_decode_cluster_launch(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, n_head, n_kv,
@@ -953,6 +960,11 @@ extern "C" int lri_attn_prefill(int dtype, const void* q, const void* k_cache, c
   LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
               "attn_prefill: pointers must be 16-byte aligned");
   if (B == 0 || S == 0) return LRI_OK;
+  const int tc_variant = option(OPT_ATTN_PREFILL_TC);
+  if (tc_variant != 0 && attn_prefill_tc_supports(B, S, n_head, n_kv, head_dim, smax))
+    return attn_prefill_tc_launch(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, S, n_head, n_kv, head_dim,
+                                  smax, kLog2e / sqrtf(static_cast<float>(head_dim)), tc_variant,
+                                  static_cast<cudaStream_t>(stream));
   PrefillParams p{};
   p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64, p.out = out;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax;

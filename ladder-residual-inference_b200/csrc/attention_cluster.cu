@@ -4,10 +4,14 @@
 // At decode batch sizes the K/V bytes of one layer are a few MB, so the kernel is a chain of
 // memory round trips, not a bandwidth problem.  The split-K form that goes through global
 // scratch pays for: partial store, fence, atomic ticket, two rounds of partial loads.  Here the
-// num_splits (1, 2, 4 or 8) CTAs that share a (batch, kv-head tile) form a cluster; each leaves
-// its (max, sum, weighted values) in its own shared memory, the cluster synchronises once, and
-// every CTA merges one slice of the output elements by reading its peers' shared memory.
-// No scratch memory, no counters, and the grid still does not depend on the position.
+// num_splits (1, 2, 4, 8 or 16) CTAs that share a (batch, kv-head tile) form a cluster.  A CTA
+// issues the loads of its whole range at once when the range is short enough (U positions per row
+// group in flight, chosen from the cache length at launch, so a 1 K context costs one DRAM round
+// trip instead of three), merges its row groups in shared memory and stores its (max, sum, weighted
+// values) straight into the shared memory of the cluster's first CTA (remote stores are fire and
+// forget, remote loads are a round trip).  After ONE cluster barrier the first CTA merges the splits
+// and writes the output; the others exit.  No scratch memory, no counters, and the grid still does
+// not depend on the position.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
@@ -21,7 +25,7 @@ namespace {
 
 constexpr int kClWarps = 8;
 constexpr int kClThreads = kClWarps * 32;
-constexpr int kClUnroll = 4;
+constexpr int kClMaxSplits = 16;
 
 struct ClusterDecodeParams {
   const void* q;        // [B, n_head, HD]
@@ -35,8 +39,16 @@ struct ClusterDecodeParams {
   float scale_log2;
 };
 
-template <typename T, int HD, int GT>
-__global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(const ClusterDecodeParams p) {
+// dynamic shared memory: [NRG][GT] max, [NRG][GT] sum, [NRG][GT][HD] values (this CTA's row groups), then the
+// splits' results as gathered in the cluster's first CTA: [16][GT][HD] values, [16][GT] max, [16][GT] sum
+template <int HD, int GT>
+constexpr int cluster_smem_bytes() {
+  constexpr int NRG = (32 / (HD / 8)) * kClWarps;
+  return (NRG * GT * (2 + HD) + kClMaxSplits * GT * (HD + 2)) * 4;
+}
+
+template <typename T, int HD, int GT, int U>
+__global__ void __launch_bounds__(kClThreads) attn_decode_cluster_kernel(const ClusterDecodeParams p) {
   constexpr int LPR = HD / 8;    // lanes per cache row
   constexpr int RPW = 32 / LPR;  // row groups per warp
   constexpr int NRG = RPW * kClWarps;
@@ -52,13 +64,13 @@ __global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(cons
   const int head0 = kvh * g + (blockIdx.y % tiles_per_kv) * GT;
   const int b = blockIdx.z;
 
-  __shared__ float sm_m[NRG][GT];
-  __shared__ float sm_l[NRG][GT];
-  __shared__ float sm_o[NRG][GT][HD];
-  // this CTA's merged result, read by the peers of the cluster
-  __shared__ __align__(16) float c_o[GT][HD];
-  __shared__ float c_m[GT];
-  __shared__ float c_l[GT];
+  extern __shared__ __align__(16) float cl_smem[];
+  float* sm_m = cl_smem;                  // [NRG][GT]
+  float* sm_l = sm_m + NRG * GT;          // [NRG][GT]
+  float* sm_o = sm_l + NRG * GT;          // [NRG][GT][HD]
+  float* g_o = sm_o + NRG * GT * HD;      // [16][GT][HD]   (used in the cluster's first CTA)
+  float* g_m = g_o + kClMaxSplits * GT * HD;  // [16][GT]
+  float* g_l = g_m + kClMaxSplits * GT;       // [16][GT]
 
   pdl_launch_dependents();
   pdl_wait();  // q and the newest cache row come from the preceding kernel
@@ -88,20 +100,21 @@ __global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(cons
   }
 
   // Warp-uniform trip count (all 32 lanes run the shuffles); rows past the end are clamped and masked.
-  for (int64_t jb = p0 + warp * RPW; jb < p1; jb += static_cast<int64_t>(NRG) * kClUnroll) {
-    uint4 kv[kClUnroll], vv[kClUnroll];
-    bool valid[kClUnroll];
+  // With U chosen at launch so that NRG * U covers the longest possible range, the loop body runs once.
+  for (int64_t jb = p0 + warp * RPW; jb < p1; jb += static_cast<int64_t>(NRG) * U) {
+    uint4 kv[U], vv[U];
+    bool valid[U];
 #pragma unroll
-    for (int t = 0; t < kClUnroll; ++t) {
+    for (int t = 0; t < U; ++t) {
       const int64_t j = jb + lane / LPR + static_cast<int64_t>(t) * NRG;
       valid[t] = j < p1;
       const int64_t jc = valid[t] ? j : p1 - 1;
       kv[t] = ld_stream16(kbase + jc * HD);
       vv[t] = ld_stream16(vbase + jc * HD);
     }
-    float s[kClUnroll][GT];
+    float s[U][GT];
 #pragma unroll
-    for (int t = 0; t < kClUnroll; ++t) {
+    for (int t = 0; t < U; ++t) {
       float kf[8];
       unpack8<T>(kv[t], kf);
 #pragma unroll
@@ -118,7 +131,7 @@ __global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(cons
     for (int h = 0; h < GT; ++h) {
       float mx = s[0][h];
 #pragma unroll
-      for (int t = 1; t < kClUnroll; ++t) mx = fmaxf(mx, s[t][h]);
+      for (int t = 1; t < U; ++t) mx = fmaxf(mx, s[t][h]);
       const float m_new = fmaxf(m[h], mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // no valid position yet: exponentials give 0
       const float corr = exp2f(m[h] - m_use);
@@ -127,10 +140,10 @@ __global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(cons
       for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
       m[h] = m_new;
 #pragma unroll
-      for (int t = 0; t < kClUnroll; ++t) s[t][h] = exp2f(s[t][h] - m_use);
+      for (int t = 0; t < U; ++t) s[t][h] = exp2f(s[t][h] - m_use);
     }
 #pragma unroll
-    for (int t = 0; t < kClUnroll; ++t) {
+    for (int t = 0; t < U; ++t) {
       float vf[8];
       unpack8<T>(vv[t], vf);
 #pragma unroll
@@ -142,81 +155,75 @@ __global__ void __launch_bounds__(kClThreads, 2) attn_decode_cluster_kernel(cons
     }
   }
 
-  // ---- merge the row groups of this CTA into c_m / c_l / c_o -----------------------------------------
+  // ---- merge the row groups of this CTA, result straight into the first CTA's gather arrays ------------
 #pragma unroll
   for (int h = 0; h < GT; ++h) {
     if (sl == 0) {
-      sm_m[rg][h] = m[h];
-      sm_l[rg][h] = l[h];
+      sm_m[rg * GT + h] = m[h];
+      sm_l[rg * GT + h] = l[h];
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) sm_o[rg][h][sl * 8 + e] = acc[h][e];
+    for (int e = 0; e < 8; ++e) sm_o[(rg * GT + h) * HD + sl * 8 + e] = acc[h][e];
   }
   __syncthreads();
+  float* r_o = cluster.map_shared_rank(g_o, 0);
+  float* r_m = cluster.map_shared_rank(g_m, 0);
+  float* r_l = cluster.map_shared_rank(g_l, 0);
   for (int idx = threadIdx.x; idx < GT * HD; idx += kClThreads) {
     const int h = idx / HD, e = idx % HD;
     float mm = -INFINITY;
 #pragma unroll
-    for (int r = 0; r < NRG; ++r) mm = fmaxf(mm, sm_m[r][h]);
+    for (int r = 0; r < NRG; ++r) mm = fmaxf(mm, sm_m[r * GT + h]);
     float ll = 0.f, oo = 0.f;
     if (mm > -INFINITY) {
 #pragma unroll
       for (int r = 0; r < NRG; ++r) {
-        const float w = exp2f(sm_m[r][h] - mm);
-        ll += sm_l[r][h] * w;
-        oo += sm_o[r][h][e] * w;
+        const float w = exp2f(sm_m[r * GT + h] - mm);
+        ll += sm_l[r * GT + h] * w;
+        oo += sm_o[(r * GT + h) * HD + e] * w;
       }
     }
-    c_o[h][e] = oo;
+    r_o[(split * GT + h) * HD + e] = oo;
     if (e == 0) {
-      c_m[h] = mm;
-      c_l[h] = ll;
+      r_m[split * GT + h] = mm;
+      r_l[split * GT + h] = ll;
     }
   }
-  cluster.sync();  // every CTA's result is in its shared memory and visible to the cluster
+  cluster.sync();  // every split's result has landed in the first CTA's shared memory
+  if (split != 0) return;
 
-  // ---- each CTA merges one slice of the GT*HD output elements over all splits -------------------------
-  const int per_cta = GT * HD / ns;  // ns is 1, 2, 4 or 8 and divides GT*HD
-  for (int i = threadIdx.x; i < per_cta; i += kClThreads) {
-    const int idx = split * per_cta + i;
+  // ---- the first CTA merges the splits -----------------------------------------------------------------
+  for (int idx = threadIdx.x; idx < GT * HD; idx += kClThreads) {
     const int h = idx / HD, e = idx % HD;
-    float pm[8], pl[8], po[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      if (r < ns) {
-        pm[r] = *cluster.map_shared_rank(&c_m[h], r);
-        pl[r] = *cluster.map_shared_rank(&c_l[h], r);
-        po[r] = *cluster.map_shared_rank(&c_o[h][e], r);
-      } else {
-        pm[r] = -INFINITY;
-        pl[r] = 0.f;
-        po[r] = 0.f;
-      }
-    }
-    float mm = pm[0];
-#pragma unroll
-    for (int r = 1; r < 8; ++r) mm = fmaxf(mm, pm[r]);
+    float mm = -INFINITY;
+    for (int r = 0; r < ns; ++r) mm = fmaxf(mm, g_m[r * GT + h]);
     float ll = 0.f, oo = 0.f;
     if (mm > -INFINITY) {
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float w = exp2f(pm[r] - mm);
-        ll += pl[r] * w;
-        oo += po[r] * w;
+      for (int r = 0; r < ns; ++r) {
+        const float w = exp2f(g_m[r * GT + h] - mm);
+        ll += g_l[r * GT + h] * w;
+        oo += g_o[(r * GT + h) * HD + e] * w;
       }
     }
     const float res = ll > 0.f ? oo / ll : 0.f;
     static_cast<T*>(p.out)[(static_cast<int64_t>(b) * p.n_head + head0 + h) * HD + e] = Num<T>::from_f(res);
   }
-  cluster.sync();  // keep this CTA's shared memory alive until every peer has read it
 }
 
-template <typename T, int HD, int GT>
+template <typename T, int HD, int GT, int U>
 int launch_one(const ClusterDecodeParams& p, int B, int ns, int tiles, cudaStream_t st) {
+  constexpr int smem = cluster_smem_bytes<HD, GT>();
+  auto kern = attn_decode_cluster_kernel<T, HD, GT, U>;
+  static std::atomic<unsigned long long> attr_set{0};  // per template instantiation, one bit per device
+  if (device_setup_needed(attr_set)) {
+    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LRI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    device_setup_done(attr_set);
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ns, tiles, B);
   cfg.blockDim = dim3(kClThreads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -227,9 +234,23 @@ int launch_one(const ClusterDecodeParams& p, int B, int ns, int tiles, cudaStrea
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  LRI_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<T, HD, GT>, p));
+  LRI_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
   LRI_LAUNCH_CHECK("attn_decode_cluster_kernel");
   return LRI_OK;
+}
+
+// U = positions per row group kept in flight: enough to cover the longest range a CTA can get
+// (ceil(smax / ns) positions over NRG row groups) in one pass when that takes at most 12, else 4 per pass.
+template <typename T, int HD, int GT>
+int launch_u(const ClusterDecodeParams& p, int B, int ns, int tiles, cudaStream_t st) {
+  constexpr int NRG = (32 / (HD / 8)) * kClWarps;
+  const int64_t longest = (p.smax + ns - 1) / ns;
+  const int64_t need = (longest + NRG - 1) / NRG;
+  if (need <= 2) return launch_one<T, HD, GT, 2>(p, B, ns, tiles, st);
+  if (need <= 4) return launch_one<T, HD, GT, 4>(p, B, ns, tiles, st);
+  if (need <= 6) return launch_one<T, HD, GT, 6>(p, B, ns, tiles, st);
+  if (need <= 8 && GT <= 2) return launch_one<T, HD, GT, 8>(p, B, ns, tiles, st);
+  return launch_one<T, HD, GT, 4>(p, B, ns, tiles, st);
 }
 
 template <typename T, int HD>
@@ -237,15 +258,16 @@ int launch_hd(const ClusterDecodeParams& p, int B, int ns, cudaStream_t st) {
   const int g = p.n_head / p.n_kv;
   const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
   const int tiles = p.n_kv * (g / gt);
-  if (gt == 4) return launch_one<T, HD, 4>(p, B, ns, tiles, st);
-  if (gt == 2) return launch_one<T, HD, 2>(p, B, ns, tiles, st);
-  return launch_one<T, HD, 1>(p, B, ns, tiles, st);
+  if (gt == 4) return launch_u<T, HD, 4>(p, B, ns, tiles, st);
+  if (gt == 2) return launch_u<T, HD, 2>(p, B, ns, tiles, st);
+  return launch_u<T, HD, 1>(p, B, ns, tiles, st);
 }
 
 }  // namespace
 
 bool attn_decode_cluster_supports(int num_splits) {
-  return option(OPT_ATTN_CLUSTER) != 0 && (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8);
+  return option(OPT_ATTN_CLUSTER) != 0 &&
+         (num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8 || num_splits == 16);
 }
 
 int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, const void* v_cache,

@@ -15,6 +15,7 @@ namespace lri {
 bool gemm_tcgen05_supports(int64_t m, int n, int k);
 int gemm_tcgen05_launch(int dtype, const void* a, const void* w, void* c, int64_t m, int n, int k, cudaStream_t st);
 int gemm_tcgen05_status_read_and_clear(int* status_out);
+int attn_prefill_tc_status_read_and_clear(int* status_out);
 bool gemm_tcgen05_fused_supports(int epi, const LinearParams& p, int64_t m);
 int gemm_tcgen05_fused_launch(int dtype, int epi, const LinearParams& p, int64_t m, cudaStream_t st);
 
@@ -42,6 +43,7 @@ const OptionSpec kOptionSpecs[OPT_COUNT] = {
     {"attn_mma", "LRI_ATTN_MMA", -1, -1, 1},
     {"decode_splits", "LRI_DECODE_SPLITS", 0, 0, 64},
     {"fused_norm", "LRI_FUSED_NORM", -1, -1, 1},
+    {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 4},
 };
 
 bool option_value_ok(int which, int v) {
@@ -318,13 +320,16 @@ extern "C" int lri_get_option(const char* name, int* value_out) {
   return fail(LRI_ERR_ARG, "get_option: unknown option '%s'", name);
 }
 extern "C" int lri_gemm_status(void) {
-  int v = 0, v2 = 0;
+  int v = 0, v2 = 0, v3 = 0;
   int rc = gemm_tcgen05_status_read_and_clear(&v);
   if (rc != LRI_OK) return rc;
   rc = gemm_streamk_status_read_and_clear(&v2);
   if (rc != LRI_OK) return rc;
+  rc = attn_prefill_tc_status_read_and_clear(&v3);
+  if (rc != LRI_OK) return rc;
   if (v != 0 || v2 != 0)
     return fail(LRI_ERR_TIMEOUT, "tcgen05 GEMM: a bounded mbarrier wait gave up (site %d)", v != 0 ? v : v2);
+  if (v3 != 0) return fail(LRI_ERR_TIMEOUT, "tcgen05 prefill attention: a bounded mbarrier wait gave up (site %d)", v3);
   return LRI_OK;
 }
 

@@ -122,7 +122,7 @@ class Engine:
         """residual += adds (in place), normed = RMSNorm(residual) * weight.  With ch1 / ch2 > 0 the
         addend is this rank's partial and the sum over ranks is gathered inside the kernel from the
         message pushed on that channel (the reduction half of the all-reduce)."""
-        res_out = self.resid if (write_residual and (add1 is not None or scale != 1.0)) else None
+        res_out = self.resid if (write_residual and (add1 is not None or add2 is not None or scale != 1.0)) else None
         out = self.normed if normed is None else normed
         if (ch1 and add1 is not None) or (ch2 and add2 is not None):
             self.comm.add_rmsnorm_gather(self.resid, ch1 if add1 is not None else 0, add1,
@@ -275,6 +275,9 @@ class Engine:
 
     # Each _run_* leaves RMSNorm(final residual) * norm.weight in self.normed.
     def _run_ladder(self, rows, B, S, pos):
+        mixed = getattr(self.cfg, "ladder_layers", None)
+        if mixed is not None and len(set(mixed)) != self.cfg.n_layer:
+            return self._run_hybrid(rows, B, S, pos, set(mixed))
         if S == 1 and self.overlap_sublayers:
             return self._run_ladder_two_streams(rows, B, S, pos)
         comm, m = self.comm, self.model
@@ -341,6 +344,43 @@ class Engine:
         comm.wait(h_a)
         comm.wait(h_m)
         self._norm(m.norm.weight, rows, add1=self.part_a, add2=self.part_m, write_residual=False, ch1=ca, ch2=cm)
+
+    def _run_hybrid(self, rows, B, S, pos, ladder):
+        """Some layers ladder, the others dense (a converted checkpoint's `ladder_layers`, reference
+        hf_modeling_utils/modeling_llama_ladder.py:627-663, 889-948).  The residual carries two pending
+        addends as in the ladder schedule; a dense layer adds both before its attention, consumes its
+        attention all-reduce at once and leaves only its MLP output pending:
+            ladder   r += P_a; A = attn(norm(r)) -> pending;  r += P_m; M = mlp(norm(r)) -> pending
+            dense    r += P_a + P_m; r += AR(attn(norm(r)));  M = mlp(norm(r)) -> pending, P_a = none"""
+        comm, m = self.comm, self.model
+        h_a = h_m = None
+        have_a = have_m = False
+        for i, layer in enumerate(m.layers):
+            if i in ladder:
+                comm.wait(h_a)
+                self._norm(layer.attention_norm.weight, rows, add1=self.part_a if have_a else None)
+                self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+                h_a = comm.all_reduce_async(self.part_a, rows)
+                comm.wait(h_m)
+                self._norm(layer.ffn_norm.weight, rows, add1=self.part_m if have_m else None)
+                self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+                h_m = comm.all_reduce_async(self.part_m, rows)
+                have_a = have_m = True
+            else:
+                comm.wait(h_a)
+                comm.wait(h_m)
+                self._norm(layer.attention_norm.weight, rows, add1=self.part_a if have_a else None,
+                           add2=self.part_m if have_m else None)
+                self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a)
+                comm.all_reduce(self.part_a, rows)
+                self._norm(layer.ffn_norm.weight, rows, add1=self.part_a)
+                self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m)
+                h_a, h_m = None, comm.all_reduce_async(self.part_m, rows)
+                have_a, have_m = False, True
+        comm.wait(h_a)
+        comm.wait(h_m)
+        self._norm(m.norm.weight, rows, add1=self.part_a if have_a else None, add2=self.part_m if have_m else None,
+                   write_residual=False)
 
     def _reduce_now(self, buf, rows, channel, split):
         """All-reduce consumed by the very next norm: pushed (and gathered there) or done in-stream."""

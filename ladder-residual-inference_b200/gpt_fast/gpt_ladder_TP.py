@@ -6,6 +6,7 @@ whole schedule in `engine.Engine`; `LadderTransformerBlock.forward` keeps the re
 block-level signature for callers that drive blocks themselves.
 """
 from dataclasses import dataclass
+from typing import List, Optional, Union
 
 import torch.distributed as dist
 from torch import Tensor
@@ -25,6 +26,19 @@ transformer_configs = family_presets("ladder")
 
 @dataclass
 class ModelArgs(ModelArgsBase):
+    # Indices of the layers that use the ladder dataflow; the others run as dense layers.  None (the
+    # default, and all the reference's gpt_fast presets): every layer is a ladder layer.  An int n means
+    # the last n layers.  This is the `ladder_layers` field of the reference's Hugging Face config
+    # (hf_modeling_utils/configuration_llama_ladder.py:38-45), needed to run converted checkpoints.
+    ladder_layers: Optional[Union[int, List[int]]] = None
+
+    def __post_init__(self):
+        super().__post_init__()
+        if isinstance(self.ladder_layers, int):
+            self.ladder_layers = list(range(self.n_layer - self.ladder_layers, self.n_layer))
+        if self.ladder_layers is not None:
+            assert all(0 <= i < self.n_layer for i in self.ladder_layers), "ladder_layers out of range"
+
     @classmethod
     def from_name(cls, name: str):
         return args_from_name(cls, transformer_configs, name)

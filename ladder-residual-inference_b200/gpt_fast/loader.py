@@ -19,8 +19,9 @@ therefore re-ordered inside every head, new row 2i + j = old row j hd/2 + i; sco
 unchanged by a permutation applied to both, and v / o_proj are untouched.
 """
 import glob
+import json
 import os
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -74,6 +75,32 @@ def hf_to_local(hf: Dict[str, Tensor], config, rank: int, world: int, family: st
         out[dst + "attention_norm.weight"] = hf[src + "input_layernorm.weight"]
         out[dst + "ffn_norm.weight"] = hf[src + "post_attention_layernorm.weight"]
     return out
+
+
+def model_args_from_hf_config(path: str) -> Dict[str, object]:
+    """ModelArgs keyword arguments from the config.json of a Hugging Face Llama / LlamaLadder
+    checkpoint directory (field names: transformers' LlamaConfig; `ladder_layers` as normalised by
+    the reference's hf_modeling_utils/configuration_llama_ladder.py:38-45).  Register the result under
+    a preset name in a family's `transformer_configs` and build the model with `from_name`."""
+    with open(os.path.join(path, "config.json") if os.path.isdir(path) else path) as f:
+        c = json.load(f)
+    n_layer = c["num_hidden_layers"]
+    kw = dict(block_size=c.get("max_position_embeddings", 2048), vocab_size=c["vocab_size"], n_layer=n_layer,
+              n_head=c["num_attention_heads"], n_local_heads=c.get("num_key_value_heads", c["num_attention_heads"]),
+              dim=c["hidden_size"], intermediate_size=c["intermediate_size"], rope_base=c.get("rope_theta", 10000.0),
+              norm_eps=c.get("rms_norm_eps", 1e-5))
+    scaling = c.get("rope_scaling")
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "llama3":
+        kw["rope_scaling"] = {k: scaling[k] for k in ("factor", "low_freq_factor", "high_freq_factor",
+                                                       "original_max_position_embeddings")}
+    if "ladder_layers" in c:
+        ll = c["ladder_layers"]
+        if ll is None:
+            ll = []
+        elif isinstance(ll, int):
+            ll = list(range(n_layer - ll, n_layer))
+        kw["ladder_layers"] = [int(i) for i in ll]
+    return kw
 
 
 def load_hf_state_dict(model, hf: Dict[str, Tensor], rank: Optional[int] = None, world: Optional[int] = None) -> None:

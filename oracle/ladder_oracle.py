@@ -49,6 +49,10 @@ class OracleConfig:
     rope_scaling: Optional[dict] = None
     reduce_pattern: Optional[List[dict]] = None
     force_disable_last_all_reduce: bool = False
+    # ladder family only: indices of the layers that use the ladder dataflow, the others are dense
+    # (hf_modeling_utils/configuration_llama_ladder.py:38-45; an int n means the last n layers).
+    # None: every layer is a ladder layer, which is what gpt_fast/gpt_ladder_TP.py runs.
+    ladder_layers: Optional[object] = None
     head_dim: int = field(init=False, default=0)
 
     def __post_init__(self):
@@ -60,6 +64,8 @@ class OracleConfig:
         self.head_dim = self.dim // self.n_head
         if self.reduce_pattern is None:
             self.reduce_pattern = [{"attention": False, "mlp": True} for _ in range(self.n_layer)]
+        if isinstance(self.ladder_layers, int):
+            self.ladder_layers = list(range(self.n_layer - self.ladder_layers, self.n_layer))
 
 
 # ----------------------------------------------------------------------------------------
@@ -309,6 +315,8 @@ class OracleModel:
     def _ladder(self, x, pos):
         """gpt_fast/gpt_ladder_TP.py:252-284, 312-358: the all-reduced output of a sublayer is
         added to the residual one sublayer later."""
+        if self.cfg.ladder_layers is not None:
+            return self._hybrid(x, pos)
         prev_a = torch.zeros_like(x)
         prev_m = torch.zeros_like(x)
         for i in range(self.cfg.n_layer):
@@ -317,6 +325,31 @@ class OracleModel:
             x = x + prev_m
             cur_m = all_reduce([self._mlp(r, i, x) for r in range(self.t)])
             prev_a, prev_m = cur_a, cur_m
+        return self._logits(x + prev_a + prev_m)
+
+    def _hybrid(self, x, pos):
+        """Checkpoints whose config lists `ladder_layers`: the listed layers use the ladder dataflow,
+        the others the dense one (hf_modeling_utils/modeling_llama_ladder.py:627-663 for a layer,
+        889-948 for the loop).  Stated on the residual stream r with two pending addends, so that
+        `hidden_states` of the reference is r + prev_a + prev_m and its `prev_attn_output` is r + prev_a:
+          ladder layer   r += prev_a; A = Attn(norm(r)); r += prev_m; M = Mlp(norm(r)); pending (A, M)
+          dense layer    r += prev_a + prev_m; r += Attn(norm(r)); M = Mlp(norm(r)); pending (0, M)
+        With every layer listed this is _ladder, with none _dense."""
+        ladder = set(self.cfg.ladder_layers)
+        prev_a = torch.zeros_like(x)
+        prev_m = torch.zeros_like(x)
+        for i in range(self.cfg.n_layer):
+            if i in ladder:
+                x = x + prev_a
+                cur_a = all_reduce([self._attn(r, i, x, pos) for r in range(self.t)])
+                x = x + prev_m
+                cur_m = all_reduce([self._mlp(r, i, x) for r in range(self.t)])
+                prev_a, prev_m = cur_a, cur_m
+            else:
+                x = (x + prev_a) + prev_m
+                x = x + all_reduce([self._attn(r, i, x, pos) for r in range(self.t)])
+                prev_a = torch.zeros_like(x)
+                prev_m = all_reduce([self._mlp(r, i, x) for r in range(self.t)])
         return self._logits(x + prev_a + prev_m)
 
     def _dense(self, x, pos):

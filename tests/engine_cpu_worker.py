@@ -63,6 +63,32 @@ def check_hf_checkpoint(rank, world, mods):
                 assert torch.isfinite(got).all() and (got - want).abs().max() > 1e-3
 
 
+def check_mixed_layers(rank, world, mods):
+    """A ladder-family model whose config lists `ladder_layers` (some layers dense): the engine's
+    hybrid step list against the oracle, prompt pass and two decode steps."""
+    import dataclasses
+    mod, cls = mods["ladder"]
+    for ladder_layers in ([1, 2], [0, 2], []):
+        cfg = dataclasses.replace(gu.tiny_config("ladder"), ladder_layers=ladder_layers)
+        full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS["loud"])
+        kw = gu.preset_kwargs(cfg)
+        kw["ladder_layers"] = ladder_layers
+        mod.transformer_configs["tiny-mixed"] = kw
+        model = cls.from_name("tiny-mixed").to(torch.float32).eval()
+        gu.load_shards(model, "ladder", cfg, full, rank, world, torch.float32)
+        model.setup_caches(max_batch_size=gu.BATCH, max_seq_length=gu.PROMPT + gu.NEW)
+        model._engine.ops = CpuOps
+        oracle = lo.OracleModel("ladder", cfg, full, world, torch.float32, gu.BATCH, gu.PROMPT + gu.NEW)
+        g = torch.Generator().manual_seed(21)
+        idx, pos = torch.randint(0, cfg.vocab_size, (gu.BATCH, gu.PROMPT), generator=g), torch.arange(gu.PROMPT)
+        for n in range(3):
+            got, want = model(idx, pos), oracle.forward(idx, pos)
+            err = gu.rel_err(got, want)
+            assert err < 2e-5, f"ladder_layers={ladder_layers} rank {rank} step {n}: {err}"
+            idx = want[:, -1].argmax(-1, keepdim=True)
+            pos = torch.tensor([gu.PROMPT + n], dtype=torch.int32)
+
+
 def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     mods = {"ladder": (gpt_ladder_TP, gpt_fast.GPTLadder), "dense": (gpt_dense_TP, gpt_fast.GPTDense),
@@ -120,6 +146,7 @@ def main():
                     assert torch.equal(got, ref_tok), f"{key} rank {rank} T={temperature} k={top_k}: " \
                                                       f"{got.flatten().tolist()} vs {ref_tok.flatten().tolist()}"
     check_hf_checkpoint(rank, world, mods)
+    check_mixed_layers(rank, world, mods)
     dist.barrier()
     if rank == 0:
         print("ENGINE-CPU-OK")

@@ -64,3 +64,56 @@ def test_ops_match_reference(dtype_name):
     q = torch.from_numpy(gold[p + "rope_x"]).to(dtype)
     out = lo.rope(q, ref_table[3:9].to(dtype)).float()
     assert torch.equal(out, torch.from_numpy(gold[p + "rope_y"]))
+
+
+def _hf_ladder_literal(model, idx, pos, ladder_layers):
+    """The reference's Hugging Face ladder model, transcribed with its own state variables
+    (hf_modeling_utils/modeling_llama_ladder.py:627-663 per layer, 889-948 for the loop):
+    `hidden` is the previous layer's mlp_output, `prev_attn` its attn_output."""
+    cfg = model.cfg
+    hidden = model.emb[idx.long()]
+    prev_attn = hidden
+    for i in range(cfg.n_layer):
+        if i not in ladder_layers:
+            attn = lo.all_reduce([model._attn(r, i, hidden, pos) for r in range(model.t)])
+            hidden = hidden + attn
+            attn_out = hidden
+            mlp = lo.all_reduce([model._mlp(r, i, hidden) for r in range(model.t)])
+            mlp_out = hidden + mlp
+        else:
+            prev_mlp = hidden
+            attn = lo.all_reduce([model._attn(r, i, prev_attn, pos) for r in range(model.t)])
+            attn_out = prev_mlp + attn
+            mlp = lo.all_reduce([model._mlp(r, i, prev_mlp) for r in range(model.t)])
+            mlp_out = attn_out + mlp
+        hidden, prev_attn = mlp_out, attn_out
+    return model._logits(hidden)
+
+
+@pytest.mark.parametrize("ladder_layers", [[], [1, 2], [0, 2], [0, 1, 2], 2])
+@pytest.mark.parametrize("tp", [1, 2])
+def test_mixed_ladder_and_dense_layers(ladder_layers, tp):
+    """Checkpoints with `ladder_layers`: the oracle's residual-plus-pending-addends form against a
+    transcription of the reference's Hugging Face loop; all layers listed is the pinned ladder
+    schedule, none the pinned dense one."""
+    import dataclasses
+    base = gu.tiny_config("ladder")
+    cfg = dataclasses.replace(base, ladder_layers=ladder_layers)
+    full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS["loud"])
+    model = lo.OracleModel("ladder", cfg, full, tp, torch.float32, gu.BATCH, gu.PROMPT + gu.NEW)
+    lit = lo.OracleModel("ladder", cfg, full, tp, torch.float32, gu.BATCH, gu.PROMPT + gu.NEW)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randint(0, cfg.vocab_size, (gu.BATCH, gu.PROMPT), generator=g)
+    pos = torch.arange(gu.PROMPT)
+    got = model.forward(x, pos)
+    want = _hf_ladder_literal(lit, x, pos, set(cfg.ladder_layers))
+    assert gu.rel_err(got, want) < 1e-5
+    tok = want[:, -1].argmax(-1, keepdim=True)
+    p1 = torch.tensor([gu.PROMPT])
+    assert gu.rel_err(model.forward(tok, p1), _hf_ladder_literal(lit, tok, p1, set(cfg.ladder_layers))) < 1e-5
+    if len(cfg.ladder_layers) == cfg.n_layer:
+        pinned = lo.OracleModel("ladder", base, full, tp, torch.float32, gu.BATCH, gu.PROMPT + gu.NEW)
+        assert torch.equal(pinned.forward(x, pos), got)
+    if len(cfg.ladder_layers) == 0:
+        pinned = lo.OracleModel("dense", base, full, tp, torch.float32, gu.BATCH, gu.PROMPT + gu.NEW)
+        assert gu.rel_err(pinned.forward(x, pos), got) < 1e-6
