@@ -72,9 +72,9 @@ def parse_args(argv=None):
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "kernels"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "kernels", "comm"],
                     help="prefill: time the prompt pass alone (tensor-core bound; an extra measurement, not the default "
-                         "metric); kernels: per-kernel table of one decode step")
+                         "metric); kernels: per-kernel table of one decode step; comm: all-reduce latency by message size")
     ap.add_argument("--head", default="vocab-parallel", choices=["replicated", "vocab-parallel"],
                     help="vocab-parallel (default): greedy choice through model.decode_greedy, the LM-head rows split over "
                          "the ranks and the arg-max fused into the projection (same tokens); replicated: the reference's "
@@ -425,7 +425,7 @@ def build_model(gpt_fast, family, preset, dtype, dev, share_with=None):
         # same parameter names and shapes (ladder, dense and desync share a module tree): the second
         # schedule runs on the very same weight tensors, no copy
         model = model.to(dtype=dtype)
-        model.load_state_dict(share_with.state_dict(), assign=True)
+        model.load_state_dict(dict(share_with.named_parameters()), assign=True)
         return model.eval()
     model = model.to(dtype=dtype).to_empty(device=dev).eval()
     torch.manual_seed(1234)  # same stream on every rank: replicated parameters are identical
@@ -848,16 +848,44 @@ def run_kernels(args):
     if hasattr(ops, "lm_head_argmax"):
         vloc = -(-s["vocab"] // (8 * t)) * 8
         add("lm_head_argmax", vloc * d * 2 + B * d * 2,
-            lambda: (rnd(B, d, scale=1), rnd(vloc, d), torch.empty(B, 2, dtype=torch.float32, device=dev),
+            lambda: (rnd(B, d, scale=1), rnd(vloc, d), torch.empty(B, dtype=torch.int32, device=dev),
                      torch.zeros(ops.lm_head_argmax_scratch_bytes(B, vloc), dtype=torch.uint8, device=dev)),
             lambda o: ops.lm_head_argmax(o[0], o[1], 0, o[2], B, o[3]))
+
+    # prompt-pass kernels (tensor-core bound; listed only when named in --only): --ctx is the prompt length
+    S = args.ctx
+    rows_p = B * S
+    tpeak, _ = measured_tensor_peak()
+    flops = {}
+
+    def add_prefill(name, fl, make, run):
+        if name in only:
+            flops[name] = fl
+            cases.append((name, 0, make, run))
+
+    add_prefill("prefill_attn", 4 * B * S * S * nh * hd // 2,
+                lambda: (rnd(rows_p, nh * hd, scale=1), rnd(B, nkv, S + 8, hd, scale=1), rnd(B, nkv, S + 8, hd, scale=1),
+                         torch.empty(B, S, nh * hd, dtype=dt, device=dev), torch.arange(S, device=dev)),
+                lambda o: ops.attention(o[0], o[1], o[2], o[4], o[3], B, S, nh, nkv, hd, None, 1))
+    add_prefill("prefill_gateup", 2 * rows_p * 2 * inter * d,
+                lambda: (rnd(rows_p, d, scale=1), rnd(2 * inter, d), torch.empty(rows_p, inter, dtype=dt, device=dev)),
+                lambda o: ops.gateup_swiglu(o[0], o[1], o[2], rows_p, None))
+    add_prefill("prefill_w2", 2 * rows_p * inter * d,
+                lambda: (rnd(rows_p, inter, scale=1), rnd(d, inter), torch.empty(rows_p, d, dtype=dt, device=dev)),
+                lambda o: ops.linear(o[0], o[1], o[2], rows_p))
+    add_prefill("prefill_add_rmsnorm", 0,
+                lambda: (rnd(rows_p, d, scale=1), rnd(rows_p, d, scale=1), rnd(d, scale=1),
+                         torch.empty(rows_p, d, dtype=dt, device=dev)),
+                lambda o: ops.add_rmsnorm(o[0], o[1], None, o[2], 1e-5, o[0], o[3], rows_p))
 
     peak, kind = measured_hbm_peak()
     rows = []
     print(f"shape {args.shape} tp {t} batch {B} ctx {args.ctx} dtype {args.dtype}; peak {peak:.0f} GB/s ({kind})")
     print(f"{'kernel':<24}{'MB/launch':>12}{'us':>10}{'GB/s':>10}{'of peak':>9}")
     for name, nbytes, make, run in cases:
-        sets = [make() for _ in range(copies(nbytes))]
+        if name == "prefill_add_rmsnorm":
+            nbytes = 5 * rows_p * d * 2
+        sets = [make() for _ in range(copies(nbytes) if not name.startswith("prefill_") else 2)]
         for o in sets:
             run(o)
         torch.cuda.synchronize()
@@ -880,6 +908,12 @@ def run_kernels(args):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(sets))
+        if name in flops and flops[name]:
+            tf = flops[name] / us / 1e6
+            rows.append(dict(kernel=name, flops=flops[name], us=us, tflops=tf, frac=tf / tpeak, copies=len(sets)))
+            print(f"{name:<24}{flops[name] / 1e9:>10.1f} GF{us:>10.2f}{tf:>8.0f} TF{tf / tpeak:>9.2f}  (of {tpeak:.0f} TFLOP/s sustained)")
+            del sets
+            continue
         gbs = nbytes / us / 1e3
         rows.append(dict(kernel=name, bytes=nbytes, us=us, gbs=gbs, frac=gbs / peak, copies=len(sets)))
         print(f"{name:<24}{nbytes / 1e6:>12.2f}{us:>10.2f}{gbs:>10.0f}{gbs / peak:>9.2f}")
@@ -888,10 +922,71 @@ def run_kernels(args):
         json.dump(dict(args=vars(args), peak=peak, peak_kind=kind, rows=rows), open(args.json, "w"), indent=1)
 
 
+def run_comm(args):
+    """All-reduce latency over message sizes for the three back ends (low-latency / one-shot peer kernel,
+    NCCL), each timed as a chain of back-to-back in-stream calls replayed from a CUDA graph; rank 0 prints
+    a table and one JSON line.  The table is what the size threshold between the peer kernel and NCCL
+    (LRI_P2P_MAX_BYTES) is chosen from."""
+    import torch
+    import torch.distributed as dist
+    import gpt_fast  # noqa: F401
+    from gpt_fast.comm import P2PComm, TorchComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    assert world > 1, "--mode comm needs at least 2 ranks"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sizes = [8 << 10, 16 << 10, 32 << 10, 64 << 10, 128 << 10, 256 << 10, 512 << 10, 1 << 20, 2 << 20, 4 << 20, 8 << 20]
+    p2p = P2PComm(max_bytes=max(sizes))
+    nccl = TorchComm()
+    chain = 20
+    out = []
+    for nbytes in sizes:
+        x = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device=dev)
+        row = {"bytes": nbytes}
+        for name, fn in (("p2p", lambda: p2p.all_reduce(x)), ("nccl", lambda: nccl.all_reduce(x))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                for _ in range(chain):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            row[name + "_us"] = ms.item() * 1e3 / (args.reps * chain)
+        out.append(row)
+    p2p.status()
+    if rank == 0:
+        print(f"all-reduce latency, {world} ranks, bf16, in-stream chain of {chain} calls per graph replay, max over ranks")
+        print(f"{'bytes':>10}{'peer kernel us':>16}{'NCCL us':>10}{'kernel':>12}")
+        for r in out:
+            kind = "LL lines" if r["bytes"] <= 128 * 1024 else "one-shot"
+            print(f"{r['bytes']:>10}{r['p2p_us']:>16.2f}{r['nccl_us']:>10.2f}{kind:>12}")
+        print(json.dumps({"mode": "comm", "n_gpus": world, "rows": out}), flush=True)
+    p2p.close()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.mode == "comm":
+        run_comm(args)
     elif args.mode == "kernels":
         run_kernels(args)
     else:

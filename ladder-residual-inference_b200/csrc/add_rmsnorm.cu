@@ -11,7 +11,9 @@ constexpr int kMaxVecPerThread = 8;  // 256 threads * 8 vectors * 8 elements = d
 
 // GATHER: an addend whose source is enabled in `g` is not read from a pointer but summed over the
 // ranks' low-latency lines (the reduction half of an all-reduce, done where the sum is used).
-template <typename T, bool GATHER>
+// NV = 16-byte vectors a thread keeps in registers (dim <= 256 * 8 * NV): sized to the row so that a
+// 4096-wide row costs a quarter of the registers of a 16384-wide one and more rows are resident per SM.
+template <typename T, bool GATHER, int NV>
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __restrict__ add1, const T* __restrict__ add2,
                    float residual_scale, const T* __restrict__ weight, float eps, T* residual_out,
@@ -24,11 +26,11 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
   uint4* ro4 = residual_out ? reinterpret_cast<uint4*>(residual_out + row * dim) : nullptr;
 
   // the norm weight is a constant of the model: fetch it while the preceding kernel drains
-  uint4 wq[kMaxVecPerThread];
+  uint4 wq[NV];
   if (weight != nullptr) {
     const uint4* w4 = reinterpret_cast<const uint4*>(weight);
 #pragma unroll
-    for (int i = 0; i < kMaxVecPerThread; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) wq[i] = __ldg(w4 + v);
     }
@@ -43,10 +45,10 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
     if (g.s2.enabled) epoch2 = *reinterpret_cast<const volatile unsigned int*>(g.s2.epoch_ptr) + 1u;
     t0 = ll_global_ns();
   }
-  float vals[kMaxVecPerThread][8];
+  float vals[NV][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerThread; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
       float x[8];
@@ -108,7 +110,7 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
   const float inv = inv_shared;
   uint4* n4 = reinterpret_cast<uint4*>(normed_out + row * dim);
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerThread; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
       float w[8], y[8];
@@ -134,28 +136,39 @@ embedding_kernel(const T* __restrict__ table, const I* __restrict__ idx, T* __re
   for (int v = threadIdx.x; v < (dim >> 3); v += blockDim.x) dst[v] = src[v];
 }
 
+template <typename T, bool GATHER, int NV>
+int launch_nv(const void* residual, const void* add1, const void* add2, float scale, const void* weight, float eps,
+              void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g, cudaStream_t st) {
+  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, GATHER, NV>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
+                      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
+                      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
+                      dim, g));
+  LRI_LAUNCH_CHECK(GATHER ? "add_rmsnorm_kernel<gather>" : "add_rmsnorm_kernel");
+  return LRI_OK;
+}
+
+template <typename T, bool GATHER>
+int launch_sized(const void* residual, const void* add1, const void* add2, float scale, const void* weight, float eps,
+                 void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g, cudaStream_t st) {
+  const int nv = (dim / 8 + kNormThreads - 1) / kNormThreads;  // vectors per thread
+  if (nv <= 1) return launch_nv<T, GATHER, 1>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
+  if (nv <= 2) return launch_nv<T, GATHER, 2>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
+  if (nv <= 4) return launch_nv<T, GATHER, 4>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
+  return launch_nv<T, GATHER, kMaxVecPerThread>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
+}
+
 template <typename T>
 int launch_add_rmsnorm(const void* residual, const void* add1, const void* add2, float scale,
                        const void* weight, float eps, void* residual_out, void* normed_out, int64_t rows,
                        int dim, cudaStream_t st) {
-  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, false>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
-                      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
-                      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
-                      dim, GatherArgs{}));
-  LRI_LAUNCH_CHECK("add_rmsnorm_kernel");
-  return LRI_OK;
+  return launch_sized<T, false>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, GatherArgs{}, st);
 }
 
 template <typename T>
 int launch_gather_typed(const void* residual, const void* add1, const void* add2, float scale, const void* weight,
                         float eps, void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g,
                         cudaStream_t st) {
-  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, true>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
-                      static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
-                      static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
-                      dim, g));
-  LRI_LAUNCH_CHECK("add_rmsnorm_kernel<gather>");
-  return LRI_OK;
+  return launch_sized<T, true>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
 }
 
 }  // namespace

@@ -44,7 +44,6 @@ struct FaParams {
   int S, n_head, n_kv;
   int64_t smax;
   float scale_log2;
-  int variant;  // 1: the layout described above; 2..4: alternative operand encodings (bring-up aid)
 };
 
 // MN-major operand tile in the 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K rows
@@ -176,9 +175,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // O += P V: A from TMEM (K-major), B MN-major (bit 16), N = HD
       constexpr uint32_t idesc_pv = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) |
                                     (static_cast<uint32_t>(HD >> 3) << 17) | (static_cast<uint32_t>(kFaM >> 4) << 24);
-      const bool swap_strides = p.variant == 3 || p.variant == 4;
-      const uint32_t v_lbo = swap_strides ? 1024u : kKvChunkBytes;  // between the 64-column chunks of head_dim
-      const uint32_t v_sbo = swap_strides ? kKvChunkBytes : 1024u;  // between groups of 8 keys
+      constexpr uint32_t v_lbo = kKvChunkBytes;  // between the 64-column chunks of head_dim
+      constexpr uint32_t v_sbo = 1024u;           // between groups of 8 keys
       bool ok = mbar_wait(q_full, 0, &abort_flag, 2, &g_attn_tc_status);
 
       auto issue_qk = [&](int j) {
@@ -224,7 +222,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int i = quarter * 32 + lane;  // query row of this thread
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const int64_t qpos = pos0 + q0 + i;
-    const bool pack_swapped = p.variant == 2 || p.variant == 4;
     float m_ref = -INFINITY, l = 0.f;
     bool alive = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -292,7 +289,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       for (int e = 0; e < 32; ++e) {
         const float p0 = exp2f(sv[2 * e] - m_use), p1 = exp2f(sv[2 * e + 1] - m_use);
         sum += p0 + p1;
-        pk[e] = pack_swapped ? pack2<T>(p1, p0) : pack2<T>(p0, p1);
+        pk[e] = pack2<T>(p0, p1);  // key 2e in the low half of column e
       }
       l += sum;
       tmem_st32(s_addr, pk);  // P over the first 32 columns of this S buffer
@@ -374,10 +371,10 @@ bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, 
 
 int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
                            int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
-                           float scale_log2, int variant, cudaStream_t st) {
+                           float scale_log2, cudaStream_t st) {
   FaParams p{};
   p.out = out, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64;
-  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2, p.variant = variant;
+  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2;
   if (dtype == LRI_BF16)
     return head_dim == 128 ? launch_fa<__nv_bfloat16, 128>(dtype, q, k_cache, v_cache, p, B, st)
                            : launch_fa<__nv_bfloat16, 64>(dtype, q, k_cache, v_cache, p, B, st);
