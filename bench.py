@@ -88,6 +88,9 @@ def parse_args(argv=None):
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly (for kernel profiling)")
     ap.add_argument("--last-logits-only", action="store_true",
                     help="prefill mode: LM head on the last position only (the reference computes every position)")
+    ap.add_argument("--trace", action="store_true",
+                    help="prefill mode: after the timed region run one more pass eagerly with per-operation CUDA-event "
+                         "timing (gpt_fast.trace) and print the table on rank 0")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU sample")
     # --mode kernels
     ap.add_argument("--shape", default="8b", choices=["1b", "8b", "70b", "405b"])
@@ -679,6 +682,20 @@ def run_prefill(args, a, model, x, comm, rank, world, dev):
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     comm.status()
     _C.check(_C.lib.lri_gemm_status())
+    if args.trace:
+        from gpt_fast.trace import trace_engine
+        tr = trace_engine(model._engine)
+        with torch.no_grad():
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            one()
+            e1.record()
+        table = tr.report()
+        tr.stop()
+        if rank == 0:
+            print(f"per-operation device time of one traced pass ({e0.elapsed_time(e1):.2f} ms in all):", file=sys.stderr)
+            for name, (n, t) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+                print(f"  {name:<28}{n:>6} calls{t:>10.2f} ms", file=sys.stderr)
     if rank != 0:
         return
     flops = prefill_flops(a, world, B, T, head_positions=1 if last_only else None)

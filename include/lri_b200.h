@@ -243,11 +243,11 @@ int lri_add_rmsnorm_gather(lri_comm* comm, int dtype, const void* residual, int 
  * index on ties, where this rank holds rows [index_offset, index_offset + N) of the output projection
  * (w [N, K]) and the other ranks of `comm` hold the rest; comm == NULL: one rank.  Logits are compared
  * as the projection would store them (fp32 sums rounded to `dtype`).  M <= 8: the weight-streaming
- * kernel folds its candidates in its epilogue and writes no logits; the CTA that finishes last
- * exchanges one 16-byte line per sequence with every peer over NVLink (bounded wait: timeout_ms,
- * status word read by lri_comm_status) and writes the winner, so projection, local arg-max, exchange
- * and global arg-max are one launch.  8 < M <= 64: the slice's logits go to logits_ws (M*N elements)
- * through lri_linear (workspace as there) and a second small kernel folds and exchanges them.
+ * kernel folds its candidates in its epilogue (one 64-bit key per sequence in `scratch`) and writes no
+ * logits.  8 < M <= 64: the slice's logits go to logits_ws (M*N elements) through lri_linear (workspace
+ * as there) and a small kernel folds them.  In both cases one warp launched behind the producer
+ * exchanges one 16-byte line per sequence with every peer over NVLink (bounded wait: timeout_ms, status
+ * word read by lri_comm_status) and writes the winner.
  * scratch: lri_lm_head_argmax_scratch_bytes() bytes, 16-byte aligned, zero before the first call;
  * every call leaves it zero.  All ranks must call with the same M; N may be 0 on a rank whose slice
  * is empty.  Every rank writes the same tokens.

@@ -3,27 +3,25 @@
 //
 // A candidate is packed into one 64-bit key, (order-preserving bits of the logit) << 32 | ~index,
 // so that the numeric maximum of keys is "largest logit, lowest index on ties".  Every CTA of the
-// producing kernel folds its candidates into one key per sequence in global memory (an atomic max
-// that is only issued when the candidate beats the current value: on random logits about ln(n)
-// times per sequence), then takes a ticket; the CTA that takes the last ticket owns the rank's
-// result.  With more than one rank it stores the keys as 16-byte lines {low, epoch, high, epoch}
-// into every peer's inbox, polls its own inbox (bounded) for the peers' lines, and the maximum over
-// ranks is the token every rank writes.  One kernel therefore does projection, local arg-max,
-// exchange and global arg-max; the keys and tickets are left at zero for the next call.
+// producing kernel folds its candidates into one key per sequence in global memory: an atomic max
+// that is only issued when the candidate beats the value it reads first (on random logits about
+// ln(n) times per sequence), so the projection's CTAs retire as fast as without it (a per-CTA
+// arrival ticket was measured to cost the 128 K-row projection 30 %: 32 K dependent atomics).  One
+// warp launched behind the projection (programmatic dependent launch) owns the rank's result: with
+// more than one rank it stores the keys as 16-byte lines {low, epoch, high, epoch} into every
+// peer's inbox, polls its own inbox (bounded) for the peers' lines, and the maximum over ranks is
+// the token every rank writes.  The keys are left at zero for the next call.
 #pragma once
 
 #include "common.cuh"
 
 namespace lri {
 
-constexpr int kArgmaxMaxRows = 64;     // sequences per call
-constexpr int kArgmaxGroup = 64;       // CTAs per first-level ticket
-constexpr int kArgmaxMaxGroups = 4096;  // first-level tickets in the scratch buffer
-constexpr size_t kArgmaxScratchBytes = kArgmaxMaxRows * 8 + 4 * (1 + kArgmaxMaxGroups);
+constexpr int kArgmaxMaxRows = 64;  // sequences per call
+constexpr size_t kArgmaxScratchBytes = kArgmaxMaxRows * 8;
 
 struct ArgmaxArgs {
   unsigned long long* keys;  // [kArgmaxMaxRows], zero between calls
-  unsigned int* tickets;     // [1 + groups]: tickets[0] counts finished groups, tickets[1 + g] the CTAs of group g
   int32_t* token_out;        // [rows]
   int64_t index_offset;      // vocabulary index of the first row of this rank's slice
   int rows;                  // sequences
@@ -50,30 +48,14 @@ __device__ __forceinline__ void argmax_offer(const ArgmaxArgs& a, int m, unsigne
   if (key > cur) atomicMax(a.keys + m, key);
 }
 
-// Two-level ticket over the CTAs of a 1-D numbering `cta` of `n_ctas`.  Call from ONE thread per CTA after
-// a __syncthreads() that follows the CTA's argmax_offer calls.  Returns true in exactly one CTA, after
-// every other CTA's offers are visible.
-__device__ __forceinline__ bool argmax_last_cta(const ArgmaxArgs& a, unsigned int cta, unsigned int n_ctas) {
-  __threadfence();
-  const unsigned int groups = (n_ctas + kArgmaxGroup - 1) / kArgmaxGroup;
-  const unsigned int g = cta / kArgmaxGroup;
-  const unsigned int in_group = (g == groups - 1) ? n_ctas - g * kArgmaxGroup : kArgmaxGroup;
-  if (atomicAdd(a.tickets + 1 + g, 1u) != in_group - 1) return false;
-  a.tickets[1 + g] = 0u;
-  __threadfence();
-  if (atomicAdd(a.tickets, 1u) != groups - 1) return false;
-  a.tickets[0] = 0u;
-  __threadfence();
-  return true;
-}
-
 __device__ __forceinline__ unsigned long long argmax_global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
 
-// Run by warp 0 of the CTA for which argmax_last_cta() returned true (all 32 lanes).
+// Run by one full warp after every producing CTA has completed (a kernel of its own behind the
+// producer, all 32 lanes).
 __device__ __forceinline__ void argmax_finish(const ArgmaxArgs& a) {
   const int lane = threadIdx.x & 31;
   unsigned int epoch = 0;

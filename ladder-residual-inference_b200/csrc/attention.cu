@@ -17,7 +17,7 @@ int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, co
 bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, int64_t smax);
 int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
                            int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
-                           float scale_log2, cudaStream_t st);
+                           float scale_log2, int poly_every, cudaStream_t st);
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -861,8 +861,8 @@ extern "C" size_t lri_attn_decode_scratch_bytes(int B, int n_head, int n_kv, int
 }
 
 // Number of sequence ranges, fixed per cache geometry so that the launch grid never depends on the
-// current position.  Up to 16 ranges (a power of two; 16 only while there are at most 8 clusters) run
-// as one thread-block cluster and merge through shared memory; that form is kept as long as a CTA then streams at most ~1 MB of K/V.
+// current position.  Up to 8 ranges (a power of two; 16 for a one- or two-cluster launch) run as one
+// thread-block cluster and merge through shared memory; that form is kept as long as a CTA then streams at most ~1 MB of K/V.
 // Longer caches take more ranges (up to 64, at least 64 positions each) and merge through the scratch
 // buffer.  The tensor-core kernel (from 128 (sequence, KV head) pairs on) takes one range per pair,
 // two only while one per pair would leave SMs without work.
@@ -887,8 +887,10 @@ extern "C" int lri_attn_decode_plan(int B, int n_head, int n_kv, int head_dim, i
   const int64_t want = (2 * sms + base - 1) / base;
   const int64_t bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8;
   if (want <= 8 || bytes_per_cta_at_8 <= (1 << 20)) {
-    // a cluster of 16 (the hardware's opt-in maximum) while at most 8 clusters are launched: one per GPC
-    const int64_t cap = (base <= 8 && attn_decode_cluster_supports(16)) ? 16 : 8;
+    // clusters of 16 (the opt-in maximum) only for one or two clusters, i.e. a one-KV-head shard of a single
+    // sequence (measured on B200, context 1152: 5.4 vs 6.7 us); with 8 clusters they are slower than 8 both
+    // alone (10.0 vs 8.3 us) and next to the MLP chain they share the SMs with
+    const int64_t cap = (base <= 2 && attn_decode_cluster_supports(16)) ? 16 : 8;
     int n = 1;
     const int64_t lim = want < cap ? want : cap;
     while (n * 2 <= lim && smax / (n * 2) >= 32) n *= 2;
@@ -960,9 +962,13 @@ extern "C" int lri_attn_prefill(int dtype, const void* q, const void* k_cache, c
   LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
               "attn_prefill: pointers must be 16-byte aligned");
   if (B == 0 || S == 0) return LRI_OK;
-  if (option(OPT_ATTN_PREFILL_TC) != 0 && attn_prefill_tc_supports(B, S, n_head, n_kv, head_dim, smax))
+  // option attn_prefill_tc: 0 = the mma.sync kernel, 1 = the tcgen05 kernel with every exponential on the
+  // special-function unit, 2..4 = the tcgen05 kernel with 1..3 of every 4 exponential pairs on the FMA pipe
+  const int tc = option(OPT_ATTN_PREFILL_TC);
+  if (tc != 0 && attn_prefill_tc_supports(B, S, n_head, n_kv, head_dim, smax))
     return attn_prefill_tc_launch(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, S, n_head, n_kv, head_dim,
-                                  smax, kLog2e / sqrtf(static_cast<float>(head_dim)), static_cast<cudaStream_t>(stream));
+                                  smax, kLog2e / sqrtf(static_cast<float>(head_dim)), tc - 1,
+                                  static_cast<cudaStream_t>(stream));
   PrefillParams p{};
   p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64, p.out = out;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax;

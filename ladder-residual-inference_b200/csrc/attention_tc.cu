@@ -44,6 +44,7 @@ struct FaParams {
   int S, n_head, n_kv;
   int64_t smax;
   float scale_log2;
+  int poly_every;  // 0: every exponential on the special-function unit; n: every n-th pair on the FMA pipe instead
 };
 
 // MN-major operand tile in the 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K rows
@@ -234,13 +235,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t s_addr = tmem_base + lane_off + sb * kSCols;
       uint32_t r0[32], r1[32];
-      tmem_ld32(s_addr, r0);
-      tmem_ld32(s_addr + 32, r1);
+      tmem_ld32_issue(s_addr, r0);
+      tmem_ld32_issue(s_addr + 32, r1);
+      tmem_wait_ld();
+      // raw scores; the softmax scale is folded into the exponent's multiply-add below
       float sv[kFaN];
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
-        sv[e] = __uint_as_float(r0[e]) * p.scale_log2;
-        sv[32 + e] = __uint_as_float(r1[e]) * p.scale_log2;
+        sv[e] = __uint_as_float(r0[e]);
+        sv[32 + e] = __uint_as_float(r1[e]);
       }
       const int64_t key0 = static_cast<int64_t>(j) * kFaN;
       // tiles that reach past the first row's position or past the end of the visible keys need the mask
@@ -251,9 +254,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           if (kj > qpos || kj >= kv_end) sv[e] = -INFINITY;
         }
       }
-      float mx = sv[0];
+      // four independent chains: a 64-long dependent max (or sum) would cost 64 instruction latencies
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int e = 1; e < kFaN; ++e) mx = fmaxf(mx, sv[e]);
+      for (int e = 4; e < kFaN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // in log2 units
       if (j == 0) {
         m_ref = mx;  // tile 0 holds key 0, which every query sees: finite
       } else {
@@ -282,15 +287,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           if (need) m_ref = mx;
         }
       }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       uint32_t pk[32];
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
-        const float p0 = exp2f(sv[2 * e] - m_use), p1 = exp2f(sv[2 * e + 1] - m_use);
-        sum += p0 + p1;
+        // the special-function unit (16 results per clock and SM, shared with the conversions below) is the
+        // busiest pipe of this kernel: a share of the exponentials is evaluated as a polynomial instead
+        const bool poly = p.poly_every != 0 && (e % 4) < p.poly_every;
+        const float a0 = fmaf(sv[2 * e], p.scale_log2, neg_m), a1 = fmaf(sv[2 * e + 1], p.scale_log2, neg_m);
+        const float p0 = poly ? exp2_poly(a0) : exp2_approx(a0);
+        const float p1 = poly ? exp2_poly(a1) : exp2_approx(a1);
+        sum4[e & 3] += p0 + p1;
         pk[e] = pack2<T>(p0, p1);  // key 2e in the low half of column e
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       tmem_st32(s_addr, pk);  // P over the first 32 columns of this S buffer
       tmem_wait_st();
@@ -371,10 +382,10 @@ bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, 
 
 int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
                            int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
-                           float scale_log2, cudaStream_t st) {
+                           float scale_log2, int poly_every, cudaStream_t st) {
   FaParams p{};
   p.out = out, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64;
-  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2;
+  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2, p.poly_every = poly_every;
   if (dtype == LRI_BF16)
     return head_dim == 128 ? launch_fa<__nv_bfloat16, 128>(dtype, q, k_cache, v_cache, p, B, st)
                            : launch_fa<__nv_bfloat16, 64>(dtype, q, k_cache, v_cache, p, B, st);

@@ -149,11 +149,18 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   Num<T>::unpack2(v.w, f[6], f[7]);
 }
 
+// two floats rounded (to nearest even) to T and packed, `lo` in the low half: one paired conversion
 template <typename T>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  T a = Num<T>::from_f(lo), b = Num<T>::from_f(hi);
-  uint16_t ua = *reinterpret_cast<uint16_t*>(&a), ub = *reinterpret_cast<uint16_t*>(&b);
-  return static_cast<uint32_t>(ua) | (static_cast<uint32_t>(ub) << 16);
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 template <typename T>
@@ -199,6 +206,31 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// 2^x by the special-function unit alone (no range fix-up: arguments here are <= 8, and results below
+// the smallest normal number may flush to zero)
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 2^x on the FMA and integer pipes (no special-function unit): round to the nearest integer with the
+// 1.5 * 2^23 trick, a degree-4 polynomial for the fraction in [-0.5, 0.5] (relative error below 6e-5, far
+// inside the rounding of a 16-bit probability), the integer part added to the exponent field.  For
+// x <= -125 the result is 0; x must stay below 128.
+__device__ __forceinline__ float exp2_poly(float x) {
+  const float xc = fmaxf(x, -125.0f);
+  const float magic = 12582912.0f;  // 1.5 * 2^23: as an integer 0x4B400000
+  const float xr = xc + magic;
+  const float f = xc - (xr - magic);
+  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
+  p = fmaf(p, f, 0.2402265070f);
+  p = fmaf(p, f, 0.6931471806f);
+  p = fmaf(p, f, 1.0f);
+  const float y = __int_as_float(__float_as_int(p) + ((__float_as_int(xr) - 0x4B400000) << 23));
+  return x <= -125.0f ? 0.0f : y;
 }
 
 // SiLU as torch evaluates it in fp32: x / (1 + exp(-x))

@@ -111,7 +111,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
   __syncthreads();
 
   if (EPI == EPI_ARGMAX) {
-    // every thread stays: the CTA synchronises again before it takes its ticket
     __shared__ unsigned long long best[M][R / 2];
     if (threadIdx.x < M * (R / 2)) {
       const int m = threadIdx.x / (R / 2), j = threadIdx.x % (R / 2);
@@ -137,11 +136,6 @@ __global__ void __launch_bounds__(kGemvMaxWarps * 32) gemv_kernel(const LinearPa
       for (int j = 1; j < R / 2; ++j) k = best[threadIdx.x][j] > k ? best[threadIdx.x][j] : k;
       argmax_offer(p.am, threadIdx.x, k);
     }
-    __syncthreads();
-    __shared__ int last;
-    if (threadIdx.x == 0) last = argmax_last_cta(p.am, blockIdx.x, gridDim.x) ? 1 : 0;
-    __syncthreads();
-    if (last && warp == 0) argmax_finish(p.am);
     return;
   }
   if (threadIdx.x >= M * (R / 2)) return;

@@ -43,7 +43,7 @@ const OptionSpec kOptionSpecs[OPT_COUNT] = {
     {"attn_mma", "LRI_ATTN_MMA", -1, -1, 1},
     {"decode_splits", "LRI_DECODE_SPLITS", 0, 0, 64},
     {"fused_norm", "LRI_FUSED_NORM", -1, -1, 1},
-    {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 1},
+    {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 4},
 };
 
 bool option_value_ok(int which, int v) {

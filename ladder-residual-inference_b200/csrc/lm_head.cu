@@ -1,7 +1,8 @@
 // Greedy decoding head: LM-head projection of this rank's vocabulary rows fused with the arg-max
-// over rows and over ranks (argmax.cuh).  Up to 8 sequences the weight-streaming GEMV computes the
-// candidates in its epilogue and no logits are written; for more sequences the logits of the
-// rank's slice come from the stream-K projection and a small kernel folds them.
+// over rows (argmax.cuh), followed by one warp that exchanges the ranks' candidates over NVLink and
+// writes the token.  Up to 8 sequences the weight-streaming GEMV folds the candidates in its
+// epilogue and no logits are written; for more sequences the logits of the rank's slice come from
+// the stream-K projection and a small kernel folds them.
 #include <cstddef>
 
 #include "linear.cuh"
@@ -51,11 +52,13 @@ __global__ void __launch_bounds__(kRowThreads) argmax_rows_kernel(const T* __res
     for (int w = 1; w < kRowThreads / 32; ++w) k = part[w] > k ? part[w] : k;
     argmax_offer(a, m, k);
   }
-  __syncthreads();
-  __shared__ int last;
-  if (threadIdx.x == 0) last = argmax_last_cta(a, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y) ? 1 : 0;
-  __syncthreads();
-  if (last && threadIdx.x < 32) argmax_finish(a);
+}
+
+// One warp: the rank's keys are final (every producing CTA has completed); exchange and write the tokens.
+__global__ void __launch_bounds__(32) argmax_finish_kernel(const ArgmaxArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  argmax_finish(a);
 }
 
 int fill_args(lri_comm* c, int64_t M, int64_t index_offset, int32_t* token_out, void* scratch, size_t scratch_bytes,
@@ -69,7 +72,6 @@ int fill_args(lri_comm* c, int64_t M, int64_t index_offset, int32_t* token_out, 
               (long long)index_offset);
   *a = ArgmaxArgs{};
   a->keys = static_cast<unsigned long long*>(scratch);
-  a->tickets = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(scratch) + kArgmaxMaxRows * 8);
   a->token_out = token_out;
   a->index_offset = index_offset;
   a->rows = static_cast<int>(M);
@@ -113,7 +115,11 @@ extern "C" int lri_lm_head_argmax(lri_comm* comm, int dtype, const void* x, cons
     LinearParams p{};
     p.x = x, p.w = w, p.m = static_cast<int>(M), p.n = N, p.k = K;
     p.am = a;
-    return gemv_launch(dtype, EPI_ARGMAX, p, st);
+    rc = gemv_launch(dtype, EPI_ARGMAX, p, st);
+    if (rc != LRI_OK) return rc;
+    LRI_CUDA(launch_pdl(argmax_finish_kernel, dim3(1), dim3(32), 0, st, a));
+    LRI_LAUNCH_CHECK("argmax_finish_kernel");
+    return LRI_OK;
   }
   // more sequences than the streaming kernel takes (or an empty slice): the logits of the slice first
   if (N > 0) {
@@ -131,5 +137,7 @@ extern "C" int lri_lm_head_argmax(lri_comm* comm, int dtype, const void* x, cons
     LRI_CUDA(launch_pdl(argmax_rows_kernel<__half>, grid, dim3(kRowThreads), 0, st, static_cast<const __half*>(logits_ws),
                         N, a));
   LRI_LAUNCH_CHECK("argmax_rows_kernel");
+  LRI_CUDA(launch_pdl(argmax_finish_kernel, dim3(1), dim3(32), 0, st, a));
+  LRI_LAUNCH_CHECK("argmax_finish_kernel");
   return LRI_OK;
 }

@@ -94,7 +94,9 @@ class Engine:
                                   os.environ.get("LRI_LADDER_OVERLAP", "1") != "0")
         if self.overlap_sublayers:
             self.normed_m = buf(self.d)
-            self.side_stream = torch.cuda.Stream()
+            # the MLP chain carries four fifths of a layer's bytes: its stream can be given the higher priority so
+            # that its CTAs are placed first and the attention chain fills what is left (LRI_SIDE_PRIORITY=-1)
+            self.side_stream = torch.cuda.Stream(priority=int(os.environ.get("LRI_SIDE_PRIORITY", "0")))
             self._events = [torch.cuda.Event() for _ in range(2 * cfg.n_layer + 2)]
         self.ready = True
 

@@ -105,8 +105,8 @@ def test_decode_splits_choice():
                 n = decode_splits(B, nh, nkv, smax)
                 assert 1 <= n <= 64 and smax // n >= 32
                 assert n in (1, 2, 4, 8, 16) or smax // n >= 64
-    assert decode_splits(1, 32, 8, 1288) == 16         # 8B, batch 1: 8 clusters of 16 CTAs, one per head tile
-    assert decode_splits(2, 32, 8, 1288) == 8          # 16 clusters: the portable cluster size
+    assert decode_splits(1, 32, 8, 1288) == 8          # 8B, batch 1: one cluster of 8 CTAs per head tile
+    assert decode_splits(1, 4, 1, 1288) == 16          # a one-KV-head shard (TP=8): a single cluster, 16 CTAs
     assert decode_splits(16, 32, 8, 1288) == 2          # 128 (sequence, KV head) pairs: tensor-core kernel, two ranges
     assert decode_splits(64, 32, 8, 1288) == 1          # 512 pairs: one range each
     assert decode_splits(64, 4, 1, 1288) == 4           # TP=8 shard: below 128 pairs, the cluster kernel

@@ -84,7 +84,7 @@ def wide_config(family):
 def ranks_agree(t, what):
     """Every rank holds bit-identical values (the all-reduces sum in a fixed order)."""
     t = t.contiguous()
-    mine = t.view(torch.int16) if t.element_size() == 2 else t
+    mine = t.view(torch.int16).to(torch.int32) if t.element_size() == 2 else t  # bit patterns; NCCL has no 16-bit integer type
     lo_, hi_ = mine.clone(), mine.clone()
     dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
