@@ -60,8 +60,8 @@ enum Option {
   OPT_ATTN_CLUSTER,     // LRI_ATTN_CLUSTER   0: decode attention never takes the thread-block-cluster kernel
   OPT_ATTN_MMA,         // LRI_ATTN_MMA       1 / 0 forces / forbids the tensor-core decode-attention kernel (-1 = choose)
   OPT_DECODE_SPLITS,    // LRI_DECODE_SPLITS  fixed number of sequence ranges for decode attention (0 = choose)
-  OPT_FUSED_NORM,       // LRI_FUSED_NORM     1 / 0 forces / forbids add + RMSNorm inside the QKV and gate/up kernels (-1 = choose)
   OPT_ATTN_PREFILL_TC,  // LRI_ATTN_PREFILL_TC  0: prefill attention on the mma.sync kernel; 1: tcgen05 / TMEM kernel (default)
+  OPT_GEMM_RESERVE_SMS, // LRI_GEMM_RESERVE_SMS  SMs the persistent prefill GEMM leaves free (for a collective running beside it)
   OPT_COUNT
 };
 int option(int which);

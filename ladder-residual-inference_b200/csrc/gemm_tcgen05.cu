@@ -398,7 +398,11 @@ int launch_tile(int dtype, const void* a, const void* w, void* c, int64_t m, int
   group = group > tiles_p ? tiles_p : group;
   GemmGrid grid{static_cast<int>(tiles_p), static_cast<int>(tiles_q), static_cast<int>(group)};
   GemmShape shape{static_cast<int>(m), n, k};
-  const int ctas = static_cast<int>(items < sm_count() ? items : sm_count());
+  // one persistent CTA per SM, minus the SMs left to a collective that runs beside the GEMM (the all-reduce
+  // of the previous sublayer in the ladder schedule: a kernel that owns every SM would keep it waiting)
+  int usable = sm_count() - option(OPT_GEMM_RESERVE_SMS);
+  usable = usable < 1 ? 1 : usable;
+  const int ctas = static_cast<int>(items < usable ? items : usable);
   LRI_CUDA(launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(kGemmThreads), static_cast<size_t>(smem), st, tp, tq,
                       static_cast<T*>(c), shape, grid, stages, lin ? *lin : LinearParams{}));
   LRI_LAUNCH_CHECK("gemm_tcgen05_kernel");
