@@ -661,12 +661,14 @@ def run_prefill(args, a, model, x, comm, rank, world, dev):
         for _ in range(W):
             one()
         launches = (_C.lib.lri_launch_count() - c0) // max(W, 1)
-        dist.barrier()
-        torch.cuda.synchronize()
         sampler = ClockSampler(torch.cuda.current_device())
         if rank == 0:
             sampler.start()
             time.sleep(0.25)
+        # the barrier comes AFTER rank 0's wait for the clock sampler: a rank that enters the timed region
+        # early would count the time it waits for the others inside its first collective
+        dist.barrier()
+        torch.cuda.synchronize()
         t0 = time.time()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -686,16 +688,21 @@ def run_prefill(args, a, model, x, comm, rank, world, dev):
         from gpt_fast.trace import trace_engine
         tr = trace_engine(model._engine)
         with torch.no_grad():
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
+            h0 = time.perf_counter()
             one()
+            host_ms = (time.perf_counter() - h0) * 1e3
             e1.record()
         table = tr.report()
         tr.stop()
         if rank == 0:
-            print(f"per-operation device time of one traced pass ({e0.elapsed_time(e1):.2f} ms in all):", file=sys.stderr)
-            for name, (n, t) in sorted(table.items(), key=lambda kv: -kv[1][1]):
-                print(f"  {name:<28}{n:>6} calls{t:>10.2f} ms", file=sys.stderr)
+            print(f"one traced pass: {e0.elapsed_time(e1):.2f} ms on the device, {host_ms:.2f} ms for the host to enqueue it",
+                  file=sys.stderr)
+            print(f"  {'operation':<28}{'calls':>6}{'device ms':>12}{'host ms':>10}", file=sys.stderr)
+            for name, (n, t, h) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+                print(f"  {name:<28}{n:>6}{t:>12.2f}{h:>10.2f}", file=sys.stderr)
     if rank != 0:
         return
     flops = prefill_flops(a, world, B, T, head_positions=1 if last_only else None)

@@ -61,7 +61,7 @@ int lri_set_gemm_backend(int backend);
  * (LRI_GEMM_GROUP), fused_prefill (LRI_FUSED_PREFILL: 0, 1), pdl (LRI_PDL: 0, 1), attn_cluster
  * (LRI_ATTN_CLUSTER: 0, 1), attn_mma (LRI_ATTN_MMA: -1 choose, 0, 1), decode_splits
  * (LRI_DECODE_SPLITS: 0 choose, 1..64), attn_prefill_tc (LRI_ATTN_PREFILL_TC: 0 mma.sync kernel, 1 tcgen05
- * kernel, 2..4 with a share of the exponentials on the FMA pipe), gemm_reserve_sms (LRI_GEMM_RESERVE_SMS: SMs
+ * kernel), gemm_reserve_sms (LRI_GEMM_RESERVE_SMS: SMs
  * the persistent prefill GEMM leaves free for a collective running beside it, 0..64).  Unknown
  * names and values an option does not take return LRI_ERR_ARG.  No counterpart in the reference
  * (its only switches are benchmark.py's command-line flags). */

@@ -17,7 +17,7 @@ int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, co
 bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, int64_t smax);
 int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
                            int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
-                           float scale_log2, int poly_every, cudaStream_t st);
+                           float scale_log2, cudaStream_t st);
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -962,13 +962,10 @@ extern "C" int lri_attn_prefill(int dtype, const void* q, const void* k_cache, c
   LRI_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out), LRI_ERR_ALIGN,
               "attn_prefill: pointers must be 16-byte aligned");
   if (B == 0 || S == 0) return LRI_OK;
-  // option attn_prefill_tc: 0 = the mma.sync kernel, 1 = the tcgen05 kernel with every exponential on the
-  // special-function unit, 2..4 = the tcgen05 kernel with 1..3 of every 4 exponential pairs on the FMA pipe
-  const int tc = option(OPT_ATTN_PREFILL_TC);
-  if (tc != 0 && attn_prefill_tc_supports(B, S, n_head, n_kv, head_dim, smax))
+  // option attn_prefill_tc: 1 = the tcgen05 / TMEM kernel (default), 0 = the mma.sync kernel below
+  if (option(OPT_ATTN_PREFILL_TC) != 0 && attn_prefill_tc_supports(B, S, n_head, n_kv, head_dim, smax))
     return attn_prefill_tc_launch(dtype, q, k_cache, v_cache, input_pos, pos_is_i64, out, B, S, n_head, n_kv, head_dim,
-                                  smax, kLog2e / sqrtf(static_cast<float>(head_dim)), tc - 1,
-                                  static_cast<cudaStream_t>(stream));
+                                  smax, kLog2e / sqrtf(static_cast<float>(head_dim)), static_cast<cudaStream_t>(stream));
   PrefillParams p{};
   p.q = q, p.k_cache = k_cache, p.v_cache = v_cache, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64, p.out = out;
   p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax;

@@ -7,7 +7,7 @@
 //                  swizzle, fetched by plain TMA loads), S in one of two TMEM buffers (64 fp32 columns)
 //   softmax        4 warps, thread i owns query row i: tcgen05.ld of its 64 scores (a row lives in one
 //                  TMEM lane, so max and sum need no shuffles), scale, causal mask, exp2 against the
-//                  running reference maximum, P rounded to the storage type and written back over S
+//                  running reference maximum (ex2.approx, scale folded into one FMA), P rounded to the storage type and written back over S
 //                  with tcgen05.st (32 columns of packed pairs)
 //   O += P V       tcgen05.mma 128 x head_dim x 64 with P read from TMEM as the A operand and the V tile
 //                  from shared memory as an MN-major B operand (V rows are keys, head_dim contiguous:
@@ -44,7 +44,6 @@ struct FaParams {
   int S, n_head, n_kv;
   int64_t smax;
   float scale_log2;
-  int poly_every;  // 0: every exponential on the special-function unit; n: every n-th pair on the FMA pipe instead
 };
 
 // MN-major operand tile in the 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K rows
@@ -292,12 +291,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
-        // the special-function unit (16 results per clock and SM, shared with the conversions below) is the
-        // busiest pipe of this kernel: a share of the exponentials is evaluated as a polynomial instead
-        const bool poly = p.poly_every != 0 && (e % 4) < p.poly_every;
-        const float a0 = fmaf(sv[2 * e], p.scale_log2, neg_m), a1 = fmaf(sv[2 * e + 1], p.scale_log2, neg_m);
-        const float p0 = poly ? exp2_poly(a0) : exp2_approx(a0);
-        const float p1 = poly ? exp2_poly(a1) : exp2_approx(a1);
+        // (evaluating a share of the exponentials as a polynomial on the FMA pipe, to unload the special-function
+        // unit, was measured slower on B200: 89 and 96 us against 84 us with a quarter and a half of them moved)
+        const float p0 = exp2_approx(fmaf(sv[2 * e], p.scale_log2, neg_m));
+        const float p1 = exp2_approx(fmaf(sv[2 * e + 1], p.scale_log2, neg_m));
         sum4[e & 3] += p0 + p1;
         pk[e] = pack2<T>(p0, p1);  // key 2e in the low half of column e
       }
@@ -382,10 +379,10 @@ bool attn_prefill_tc_supports(int B, int S, int n_head, int n_kv, int head_dim, 
 
 int attn_prefill_tc_launch(int dtype, const void* q, const void* k_cache, const void* v_cache, const void* input_pos,
                            int pos_is_i64, void* out, int B, int S, int n_head, int n_kv, int head_dim, int64_t smax,
-                           float scale_log2, int poly_every, cudaStream_t st) {
+                           float scale_log2, cudaStream_t st) {
   FaParams p{};
   p.out = out, p.input_pos = input_pos, p.pos_is_i64 = pos_is_i64;
-  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2, p.poly_every = poly_every;
+  p.S = S, p.n_head = n_head, p.n_kv = n_kv, p.smax = smax, p.scale_log2 = scale_log2;
   if (dtype == LRI_BF16)
     return head_dim == 128 ? launch_fa<__nv_bfloat16, 128>(dtype, q, k_cache, v_cache, p, B, st)
                            : launch_fa<__nv_bfloat16, 64>(dtype, q, k_cache, v_cache, p, B, st);

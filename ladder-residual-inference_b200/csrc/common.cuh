@@ -216,23 +216,6 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
-// 2^x on the FMA and integer pipes (no special-function unit): round to the nearest integer with the
-// 1.5 * 2^23 trick, a degree-4 polynomial for the fraction in [-0.5, 0.5] (relative error below 6e-5, far
-// inside the rounding of a 16-bit probability), the integer part added to the exponent field.  For
-// x <= -125 the result is 0; x must stay below 128.
-__device__ __forceinline__ float exp2_poly(float x) {
-  const float xc = fmaxf(x, -125.0f);
-  const float magic = 12582912.0f;  // 1.5 * 2^23: as an integer 0x4B400000
-  const float xr = xc + magic;
-  const float f = xc - (xr - magic);
-  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
-  p = fmaf(p, f, 0.2402265070f);
-  p = fmaf(p, f, 0.6931471806f);
-  p = fmaf(p, f, 1.0f);
-  const float y = __int_as_float(__float_as_int(p) + ((__float_as_int(xr) - 0x4B400000) << 23));
-  return x <= -125.0f ? 0.0f : y;
-}
-
 // SiLU as torch evaluates it in fp32: x / (1 + exp(-x))
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 

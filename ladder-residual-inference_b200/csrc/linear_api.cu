@@ -42,7 +42,7 @@ const OptionSpec kOptionSpecs[OPT_COUNT] = {
     {"attn_cluster", "LRI_ATTN_CLUSTER", 1, 0, 1},
     {"attn_mma", "LRI_ATTN_MMA", -1, -1, 1},
     {"decode_splits", "LRI_DECODE_SPLITS", 0, 0, 64},
-    {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 4},
+    {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 1},
     {"gemm_reserve_sms", "LRI_GEMM_RESERVE_SMS", 0, 0, 64},
 };
 

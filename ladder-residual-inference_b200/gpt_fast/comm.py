@@ -24,6 +24,14 @@ import torch.distributed as dist
 P2P_MAX_BYTES_DEFAULT = 2 * 1024 * 1024
 
 
+def p2p_max_bytes(world):
+    """Largest message the peer all-reduce kernels take before NCCL does, from the measured latency table
+    (`bench.py --mode comm` on one 8 x B200 host): with 2 ranks the one-shot kernel wins up to the 8 MiB
+    measured (30.9 vs 42.8 us at 4 MiB), with 8 ranks every rank pushes 7 copies and NCCL wins from 2 MiB
+    on (45.6 vs 37.9 us) while the kernel wins at 1 MiB (31.6 vs 34.6 us); 4 ranks take the value between."""
+    return {2: 8 << 20, 3: 4 << 20, 4: 2 << 20}.get(world, 1 << 20 if world > 4 else 8 << 20)
+
+
 class NoComm:
     world = 1
     rank = 0
@@ -235,7 +243,7 @@ def make_comm():
     use_p2p = mode in ("auto", "p2p") and torch.cuda.is_available() and dist.get_backend() == "nccl" and world <= 8
     if use_p2p:
         try:
-            _COMM = P2PComm(max_bytes=int(os.environ.get("LRI_P2P_MAX_BYTES", P2P_MAX_BYTES_DEFAULT)))
+            _COMM = P2PComm(max_bytes=int(os.environ.get("LRI_P2P_MAX_BYTES", p2p_max_bytes(world))))
         except RuntimeError:
             if mode == "p2p":
                 raise

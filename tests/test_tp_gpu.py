@@ -23,5 +23,6 @@ def test_tp_worker(world):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=1200, env=env)
     sys.stdout.write(r.stdout[-4000:])
-    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    failures = "\n".join(line for line in (r.stdout + r.stderr).splitlines() if "TP-GPU-FAIL" in line)[:4000]
+    assert r.returncode == 0, failures + "\n" + r.stdout[-2000:] + r.stderr[-2000:]
     assert f"TP-GPU-OK world={world}" in r.stdout

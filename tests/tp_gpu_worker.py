@@ -98,6 +98,10 @@ def check_wide_models(comm_name, split):
     os.environ["LRI_COMM"] = comm_name
     os.environ["LRI_SPLIT_AR"] = "1" if split else "0"
     comm_mod.reset_comm()
+    # The peer kernels sum the ranks' partials in fp32 and round once, as the oracle does.  NCCL adds 16-bit
+    # partials hop by hop (world - 1 roundings), which the oracle does not model: from 4 ranks on its leg gets
+    # twice the bound, and the ranks must still agree bit for bit.
+    tol = 2e-2 if (comm_name == "p2p" or world <= 2) else 4e-2
     for family in gu.FAMILIES:
         cfg = wide_config(family)
         full = lo.make_full_weights(cfg, 909, std=0.05, norm_mean=1.0, norm_std=0.1)
@@ -119,12 +123,13 @@ def check_wide_models(comm_name, split):
                     ranks_agree(logits, what)
                     one = single.forward(idx, pos).float()
                     e1 = gu.rel_err(got[:, -1], one[:, -1])
-                    assert e1 < 2e-2, f"{what}: {e1:.3e} from the one-rank oracle"
+                    assert e1 < tol, f"{what}: {e1:.3e} from the one-rank oracle"
                 if family != "desync" or rank == 0:
                     err = gu.rel_err(got[:, -1], ref[:, -1])
-                    assert err < 2e-2, f"{what}: rel err {err:.3e}"
+                    assert err < tol, f"{what}: rel err {err:.3e}"
                     if n == 0:
-                        assert gu.rel_err(got, ref) < 2e-2, f"{what}: prompt pass, all positions"
+                        e0 = gu.rel_err(got, ref)
+                        assert e0 < tol, f"{what}: prompt pass, all positions: {e0:.3e}"
                 if family != "desync" and n == WIDE_NEW - 1:
                     with torch.no_grad():
                         tok = model.decode_greedy(idx.to(dev), pos.to(dev))
@@ -334,10 +339,10 @@ def check_bounded_wait():
 def main():
     c = check_p2p_allreduce()
     c.close()
-    check_wide_models("nccl", split=False)
-    check_wide_models("p2p", split=True)    # push after the projection, reduction inside the next add + norm
     check_wide_models("p2p", split=False)   # stand-alone all-reduce kernel
+    check_wide_models("p2p", split=True)    # push after the projection, reduction inside the next add + norm
     check_wide_graph()
+    check_wide_models("nccl", split=False)
     if world == 2:  # the reference's own TP = 2 fixtures (a 2-KV-head model) and the two-rank timeout scenario
         check_models("nccl")
         check_models("p2p", split=True)
@@ -350,4 +355,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException as e:  # one line that survives the launcher's own summary of the failure
+        print(f"TP-GPU-FAIL rank {rank}: {type(e).__name__}: {str(e)[:500]}", flush=True)
+        raise
