@@ -209,3 +209,41 @@ def test_engine_schedules_on_cpu_ranks(world):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "ENGINE-CPU-OK" in r.stdout
+
+
+def test_message_size_threshold_and_elided_comm():
+    """Host logic of the communicator module: the peer-kernel / NCCL size threshold per world size (from the
+    measured latency table) and the comm-elided stand-in used to measure the exposed all-reduce time."""
+    from gpt_fast.comm import ElidedComm, p2p_max_bytes
+    assert p2p_max_bytes(2) == 8 << 20 and p2p_max_bytes(4) == 2 << 20 and p2p_max_bytes(8) == 1 << 20
+    # every decode message of the benchmark configurations stays on the peer kernels at 8 ranks
+    for batch, dim in ((1, 4096), (16, 4096), (64, 8192), (16, 16384)):
+        assert batch * dim * 2 <= p2p_max_bytes(8)
+
+    class Like:
+        handle, timeout_ms = object(), 123
+
+    e = ElidedComm(8, 3, like=Like)
+    assert (e.world, e.rank, e.handle, e.timeout_ms) == (8, 3, Like.handle, 123)
+    assert e.all_reduce_async(None) is None and e.wait(None) is None and not e.can_split(8, 1)
+
+
+def test_model_args_from_hf_config(tmp_path):
+    """config.json of a Hugging Face Llama / LlamaLadder checkpoint -> ModelArgs keyword arguments, with the
+    reference's normalisation of `ladder_layers` (an int means the last n layers)."""
+    import json
+    from gpt_fast.loader import model_args_from_hf_config
+    cfg = dict(vocab_size=1000, hidden_size=256, intermediate_size=512, num_hidden_layers=6, num_attention_heads=4,
+               num_key_value_heads=2, rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=4096,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192), ladder_layers=2)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    kw = model_args_from_hf_config(str(tmp_path))
+    assert kw["ladder_layers"] == [4, 5] and kw["n_local_heads"] == 2 and kw["block_size"] == 4096
+    assert kw["rope_scaling"]["factor"] == 8.0 and "rope_type" not in kw["rope_scaling"]
+    from gpt_fast import gpt_ladder_TP
+    args = gpt_ladder_TP.ModelArgs(**kw)
+    assert args.ladder_layers == [4, 5] and args.head_dim == 64
+    cfg.pop("ladder_layers")
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    assert "ladder_layers" not in model_args_from_hf_config(str(tmp_path / "config.json"))
