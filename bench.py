@@ -962,38 +962,62 @@ def run_comm(args):
     p2p = P2PComm(max_bytes=max(sizes))
     nccl = TorchComm()
     chain = 20
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            for _ in range(chain):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() * 1e3 / (args.reps * chain)
+
     out = []
     for nbytes in sizes:
         x = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device=dev)
         row = {"bytes": nbytes}
         for name, fn in (("p2p", lambda: p2p.all_reduce(x)), ("nccl", lambda: nccl.all_reduce(x))):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            dist.barrier()
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                fn()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            with torch.cuda.graph(graph):
-                for _ in range(chain):
-                    fn()
-            graph.replay()
-            torch.cuda.synchronize()
-            dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.reps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            row[name + "_us"] = ms.item() * 1e3 / (args.reps * chain)
+            row[name + "_us"] = timed(fn)
         out.append(row)
+
+    # all-reduce + residual add + RMSNorm of a decode step: the all-reduce kernel followed by the norm
+    # kernel, against the one kernel that does both (lri_add_rmsnorm_allreduce)
+    from gpt_fast.ops import CudaOps as ops
+    fused = []
+    for rows, dim in ((1, 4096), (1, 8192), (8, 4096), (16, 4096), (8, 8192)):
+        part = torch.zeros(rows, dim, dtype=torch.bfloat16, device=dev)
+        resid = torch.zeros(rows, dim, dtype=torch.bfloat16, device=dev)
+        normed = torch.empty_like(resid)
+        w = torch.ones(dim, dtype=torch.bfloat16, device=dev)
+
+        def two():
+            p2p.all_reduce(part)
+            ops.add_rmsnorm(resid, part, None, w, 1e-5, resid, normed, rows, 1.0)
+
+        def one():
+            p2p.add_rmsnorm_gather(resid, 1, part, 0, None, w, 1e-5, resid, normed, rows, 1.0, self_push=True)
+
+        fused.append({"rows": rows, "dim": dim, "allreduce_then_norm_us": timed(two), "fused_us": timed(one),
+                      "norm_only_us": timed(lambda: ops.add_rmsnorm(resid, part, None, w, 1e-5, resid, normed, rows, 1.0))})
     p2p.status()
     if rank == 0:
         print(f"all-reduce latency, {world} ranks, bf16, in-stream chain of {chain} calls per graph replay, max over ranks")
@@ -1001,7 +1025,11 @@ def run_comm(args):
         for r in out:
             kind = "LL lines" if r["bytes"] <= 128 * 1024 else "one-shot"
             print(f"{r['bytes']:>10}{r['p2p_us']:>16.2f}{r['nccl_us']:>10.2f}{kind:>12}")
-        print(json.dumps({"mode": "comm", "n_gpus": world, "rows": out}), flush=True)
+        print(f"all-reduce + add + RMSNorm, {world} ranks, bf16, same chain")
+        print(f"{'rows':>6}{'dim':>7}{'kernel + norm us':>18}{'one kernel us':>15}{'norm alone us':>15}")
+        for r in fused:
+            print(f"{r['rows']:>6}{r['dim']:>7}{r['allreduce_then_norm_us']:>18.2f}{r['fused_us']:>15.2f}{r['norm_only_us']:>15.2f}")
+        print(json.dumps({"mode": "comm", "n_gpus": world, "rows": out, "fused_norm": fused}), flush=True)
     p2p.close()
 
 

@@ -240,6 +240,18 @@ int lri_add_rmsnorm_gather(lri_comm* comm, int dtype, const void* residual, int 
                            const void* add1, int channel2, const void* add2, float residual_scale,
                            const void* weight, float eps, void* residual_out, void* normed_out,
                            int64_t rows, int dim, int timeout_ms, lri_stream_t stream);
+/* lri_add_rmsnorm_allreduce: the whole all-reduce inside the consumer.  Same arguments and result as
+ * lri_add_rmsnorm_gather, but nothing is pushed beforehand: every thread of the kernel first stores
+ * the elements of this rank's partial(s) it is about to sum into the peers' inboxes and then polls
+ * for theirs, so all-reduce + residual add + RMSNorm cost one launch on the consuming stream (no
+ * all-reduce kernel, no communication stream, no event hop).  Channels, epochs, message limit and
+ * ordering rule are those of the push channels; a channel carries either pushed or self-pushed
+ * messages, all ranks alike.
+ * Replaces: all_reduce_func + residual add + RMSNorm, gpt_fast/gpt_ladder_TP.py:323-356. */
+int lri_add_rmsnorm_allreduce(lri_comm* comm, int dtype, const void* residual, int channel1,
+                              const void* add1, int channel2, const void* add2, float residual_scale,
+                              const void* weight, float eps, void* residual_out, void* normed_out,
+                              int64_t rows, int dim, int timeout_ms, lri_stream_t stream);
 /* ---- greedy decoding head: LM-head projection + arg-max over vocabulary rows and ranks ---------
  * token_out[m] (int32) = index of the largest logit of sequence m over the whole vocabulary, lowest
  * index on ties, where this rank holds rows [index_offset, index_offset + N) of the output projection

@@ -6,15 +6,18 @@
 namespace lri {
 namespace {
 
-constexpr int kNormThreads = 256;
+constexpr int kNormThreads = 256;    // threads of a CTA when there are many rows (prompt pass)
 constexpr int kMaxVecPerThread = 8;  // 256 threads * 8 vectors * 8 elements = dim up to 16384
+constexpr int kFewRows = 16;         // up to here a row gets up to 1024 threads: the kernel is a latency chain
 
 // GATHER: an addend whose source is enabled in `g` is not read from a pointer but summed over the
 // ranks' low-latency lines (the reduction half of an all-reduce, done where the sum is used).
-// NV = 16-byte vectors a thread keeps in registers (dim <= 256 * 8 * NV): sized to the row so that a
+// NV = 16-byte vectors a thread keeps in registers (dim <= THREADS * 8 * NV): sized to the row so that a
 // 4096-wide row costs a quarter of the registers of a 16384-wide one and more rows are resident per SM.
-template <typename T, bool GATHER, int NV>
-__global__ void __launch_bounds__(kNormThreads)
+// THREADS: 256 for many rows; a decode step has a handful of rows, one CTA each, and the kernel's
+// duration is the latency of one thread's loads and polls, so the row is spread over up to 1024 threads.
+template <typename T, bool GATHER, int NV, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __restrict__ add1, const T* __restrict__ add2,
                    float residual_scale, const T* __restrict__ weight, float eps, T* residual_out,
                    T* __restrict__ normed_out, int dim, const GatherArgs g) {
@@ -31,11 +34,15 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
     const uint4* w4 = reinterpret_cast<const uint4*>(weight);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int v = threadIdx.x + i * kNormThreads;
+      const int v = threadIdx.x + i * THREADS;
       if (v < nvec) wq[i] = __ldg(w4 + v);
     }
   }
-  pdl_launch_dependents();
+  // A kernel that gathers from the peers waits for NVLink: dependents launched now would sit resident
+  // on the SMs for that long and take them from the kernels of the other stream.  It lets them go
+  // once the peers' lines have arrived.
+  const bool waits_for_peers = GATHER && (g.s1.enabled || g.s2.enabled);
+  if (!waits_for_peers) pdl_launch_dependents();
   pdl_wait();  // the residual and the addends come from the preceding kernels
   unsigned int epoch1 = 0, epoch2 = 0;
   unsigned long long t0 = 0;
@@ -44,12 +51,24 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
     if (g.s1.enabled) epoch1 = *reinterpret_cast<const volatile unsigned int*>(g.s1.epoch_ptr) + 1u;
     if (g.s2.enabled) epoch2 = *reinterpret_cast<const volatile unsigned int*>(g.s2.epoch_ptr) + 1u;
     t0 = ll_global_ns();
+    // a consumer that is its own producer sends everything it owns before it waits for anything
+    if ((g.s1.enabled && g.s1.push) || (g.s2.enabled && g.s2.push)) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+          const int64_t elem = row * dim + static_cast<int64_t>(v) * 8;
+          if (g.s1.enabled && g.s1.push) ll_push8<T>(g.s1, epoch1, elem);
+          if (g.s2.enabled && g.s2.push) ll_push8<T>(g.s2, epoch2, elem);
+        }
+      }
+    }
   }
   float vals[NV][8];
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
+    const int v = threadIdx.x + i * THREADS;
     if (v < nvec) {
       float x[8];
       unpack8<T>(r4[v], x);
@@ -87,6 +106,7 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
       }
     }
   }
+  if (waits_for_peers) pdl_launch_dependents();
   if (GATHER) {
     __syncthreads();  // every thread of this CTA has finished reading the peers' lines
     if (threadIdx.x == 0) {
@@ -96,13 +116,13 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
   }
   if (normed_out == nullptr) return;
 
-  __shared__ float warp_part[kNormThreads / 32];
+  __shared__ float warp_part[THREADS / 32];
   __shared__ float inv_shared;
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float t = threadIdx.x < kNormThreads / 32 ? warp_part[threadIdx.x] : 0.f;
+    float t = threadIdx.x < THREADS / 32 ? warp_part[threadIdx.x] : 0.f;
     t = warp_sum(t);
     if (threadIdx.x == 0) inv_shared = rsqrtf(t / static_cast<float>(dim) + eps);
   }
@@ -111,7 +131,7 @@ add_rmsnorm_kernel(const T* residual /* may alias residual_out */, const T* __re
   uint4* n4 = reinterpret_cast<uint4*>(normed_out + row * dim);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
+    const int v = threadIdx.x + i * THREADS;
     if (v < nvec) {
       float w[8], y[8];
       unpack8<T>(wq[i], w);
@@ -136,10 +156,10 @@ embedding_kernel(const T* __restrict__ table, const I* __restrict__ idx, T* __re
   for (int v = threadIdx.x; v < (dim >> 3); v += blockDim.x) dst[v] = src[v];
 }
 
-template <typename T, bool GATHER, int NV>
+template <typename T, bool GATHER, int NV, int THREADS>
 int launch_nv(const void* residual, const void* add1, const void* add2, float scale, const void* weight, float eps,
               void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g, cudaStream_t st) {
-  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, GATHER, NV>, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, st,
+  LRI_CUDA(launch_pdl(add_rmsnorm_kernel<T, GATHER, NV, THREADS>, dim3(static_cast<unsigned>(rows)), dim3(THREADS), 0, st,
                       static_cast<const T*>(residual), static_cast<const T*>(add1), static_cast<const T*>(add2), scale,
                       static_cast<const T*>(weight), eps, static_cast<T*>(residual_out), static_cast<T*>(normed_out),
                       dim, g));
@@ -150,11 +170,26 @@ int launch_nv(const void* residual, const void* add1, const void* add2, float sc
 template <typename T, bool GATHER>
 int launch_sized(const void* residual, const void* add1, const void* add2, float scale, const void* weight, float eps,
                  void* residual_out, void* normed_out, int64_t rows, int dim, const GatherArgs& g, cudaStream_t st) {
-  const int nv = (dim / 8 + kNormThreads - 1) / kNormThreads;  // vectors per thread
-  if (nv <= 1) return launch_nv<T, GATHER, 1>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
-  if (nv <= 2) return launch_nv<T, GATHER, 2>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
-  if (nv <= 4) return launch_nv<T, GATHER, 4>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
-  return launch_nv<T, GATHER, kMaxVecPerThread>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st);
+#define LRI_NORM(NV, THREADS) \
+  return launch_nv<T, GATHER, NV, THREADS>(residual, add1, add2, scale, weight, eps, residual_out, normed_out, rows, dim, g, st)
+  const int nvec = dim / 8;
+  if (rows <= kFewRows && nvec > kNormThreads) {
+    if (nvec <= 512) LRI_NORM(1, 512);
+    if constexpr (GATHER) {
+      // the polling code keeps the peers' lines of a vector in registers: 512 threads is what fits without spilling
+      if (nvec <= 1024) LRI_NORM(2, 512);
+      LRI_NORM(4, 512);
+    } else {
+      if (nvec <= 1024) LRI_NORM(1, 1024);
+      LRI_NORM(2, 1024);
+    }
+  }
+  const int nv = (nvec + kNormThreads - 1) / kNormThreads;  // vectors per thread
+  if (nv <= 1) LRI_NORM(1, kNormThreads);
+  if (nv <= 2) LRI_NORM(2, kNormThreads);
+  if (nv <= 4) LRI_NORM(4, kNormThreads);
+  LRI_NORM(kMaxVecPerThread, kNormThreads);
+#undef LRI_NORM
 }
 
 template <typename T>

@@ -370,8 +370,9 @@ extern "C" int lri_linear_push(lri_comm* c, int channel, int dtype, const void* 
   return gemv_launch(dtype, EPI_PLAIN, p, static_cast<cudaStream_t>(stream));
 }
 
-static int fill_source(lri_comm* c, int channel, const void* own, int64_t count, int timeout_ms, LlSource* s) {
+static int fill_source(lri_comm* c, int channel, const void* own, int64_t count, int timeout_ms, bool push, LlSource* s) {
   s->enabled = 0;
+  s->push = 0;
   if (channel <= 0) return LRI_OK;
   LRI_REQUIRE(channel <= kPushChannels, LRI_ERR_ARG, "add_rmsnorm_gather: channel %d outside 1..%d", channel,
               kPushChannels);
@@ -389,13 +390,19 @@ static int fill_source(lri_comm* c, int channel, const void* own, int64_t count,
   s->timeout_ns = static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull;
   s->world = c->world, s->rank = c->rank;
   s->enabled = 1;
+  if (push) {
+    for (int r = 0; r < c->world; ++r) {
+      LRI_REQUIRE(c->peer[r] != nullptr, LRI_ERR_ARG, "add_rmsnorm_allreduce: peer %d is not connected", r);
+      s->peer_region[r] = c->peer[r] + ll_region(c->world, c->max_bytes, channel);
+    }
+    s->push = 1;
+  }
   return LRI_OK;
 }
 
-extern "C" int lri_add_rmsnorm_gather(lri_comm* c, int dtype, const void* residual, int channel1, const void* add1,
-                                      int channel2, const void* add2, float residual_scale, const void* weight,
-                                      float eps, void* residual_out, void* normed_out, int64_t rows, int dim,
-                                      int timeout_ms, lri_stream_t stream) {
+static int gather_norm(lri_comm* c, int dtype, const void* residual, int channel1, const void* add1, int channel2,
+                       const void* add2, float residual_scale, const void* weight, float eps, void* residual_out,
+                       void* normed_out, int64_t rows, int dim, int timeout_ms, bool push, lri_stream_t stream) {
   LRI_REQUIRE(c && residual, LRI_ERR_ARG, "add_rmsnorm_gather: NULL argument");
   LRI_REQUIRE(dtype == LRI_BF16 || dtype == LRI_FP16, LRI_ERR_UNSUPPORTED, "add_rmsnorm_gather: dtype %d", dtype);
   LRI_REQUIRE(rows >= 0 && rows < (1ll << 31) && dim > 0, LRI_ERR_ARG, "add_rmsnorm_gather: rows=%lld dim=%d",
@@ -407,12 +414,30 @@ extern "C" int lri_add_rmsnorm_gather(lri_comm* c, int dtype, const void* residu
                   aligned16(residual_out) && aligned16(normed_out),
               LRI_ERR_ALIGN, "add_rmsnorm_gather: pointers must be 16-byte aligned");
   GatherArgs g{};
-  int rc = fill_source(c, channel1, add1, rows * dim, timeout_ms, &g.s1);
+  int rc = fill_source(c, channel1, add1, rows * dim, timeout_ms, push, &g.s1);
   if (rc != LRI_OK) return rc;
-  rc = fill_source(c, channel2, add2, rows * dim, timeout_ms, &g.s2);
+  rc = fill_source(c, channel2, add2, rows * dim, timeout_ms, push, &g.s2);
   if (rc != LRI_OK) return rc;
   return launch_add_rmsnorm_gather(dtype, residual, add1, add2, residual_scale, weight, eps, residual_out, normed_out,
                                    rows, dim, g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lri_add_rmsnorm_gather(lri_comm* c, int dtype, const void* residual, int channel1, const void* add1,
+                                      int channel2, const void* add2, float residual_scale, const void* weight,
+                                      float eps, void* residual_out, void* normed_out, int64_t rows, int dim,
+                                      int timeout_ms, lri_stream_t stream) {
+  return gather_norm(c, dtype, residual, channel1, add1, channel2, add2, residual_scale, weight, eps, residual_out,
+                     normed_out, rows, dim, timeout_ms, false, stream);
+}
+
+// All-reduce + add + RMSNorm in one launch: as lri_add_rmsnorm_gather, but nothing has been pushed
+// beforehand; the kernel stores this rank's partials into the peers' inboxes itself before it polls.
+extern "C" int lri_add_rmsnorm_allreduce(lri_comm* c, int dtype, const void* residual, int channel1, const void* add1,
+                                         int channel2, const void* add2, float residual_scale, const void* weight,
+                                         float eps, void* residual_out, void* normed_out, int64_t rows, int dim,
+                                         int timeout_ms, lri_stream_t stream) {
+  return gather_norm(c, dtype, residual, channel1, add1, channel2, add2, residual_scale, weight, eps, residual_out,
+                     normed_out, rows, dim, timeout_ms, true, stream);
 }
 
 extern "C" int lri_comm_status(lri_comm* c, lri_stream_t stream) {

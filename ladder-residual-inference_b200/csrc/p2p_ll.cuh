@@ -5,6 +5,9 @@
 // the lines of its own inbox for the elements it is about to use and sums them in rank order
 // together with its own partial.  The fused add + RMSNorm kernel does exactly that, so that an
 // all-reduce costs the compute stream one small push kernel and no kernel on the consumer side.
+// With `push` set the consumer is its own producer as well: every thread first stores the elements
+// it is about to sum into the peers' inboxes and then polls for theirs, which makes the kernel a
+// complete all-reduce + add + RMSNorm in one launch (no producer kernel, no stream hop).
 #pragma once
 
 #include "common.cuh"
@@ -17,10 +20,12 @@ struct LlSource {
   unsigned int* ticket_ptr;       // arrival counter of the consumer's CTAs (self-resetting)
   int* status_ptr;                // receives LRI_ERR_TIMEOUT when a bounded poll gives up
   const void* own;                // this rank's own partial (same layout as the message)
+  uint8_t* peer_region[8];        // push != 0: the channel's line region in every rank's inbox, as mapped here
   int64_t slot_bytes;             // bytes of one (buffer, source rank) slot
   unsigned long long timeout_ns;
   int world, rank;
   int enabled;
+  int push;                       // the consumer stores its own partial to the peers before it polls
 };
 
 struct GatherArgs {
@@ -39,6 +44,25 @@ __device__ __forceinline__ unsigned long long ll_global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+// Producer step of a consumer that is its own producer: 8 consecutive elements of this rank's
+// partial, starting at flat element index `elem` (a multiple of 8), go as two lines into slot `rank`
+// of every peer's region.
+template <typename T>
+__device__ __forceinline__ void ll_push8(const LlSource& s, unsigned int epoch, int64_t elem) {
+  const uint4 own = *reinterpret_cast<const uint4*>(static_cast<const T*>(s.own) + elem);
+  const size_t off = (static_cast<size_t>(epoch & 1u) * s.world + s.rank) * s.slot_bytes + (elem >> 2) * 16;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {  // constant indices: the argument block is not copied to local memory
+    if (r >= s.world || r == s.rank) continue;
+    uint8_t* dst = s.peer_region[r] + off;
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(own.x), "r"(epoch), "r"(own.y), "r"(epoch)
+                 : "memory");
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 16), "r"(own.z), "r"(epoch), "r"(own.w),
+                 "r"(epoch)
+                 : "memory");
+  }
 }
 
 // Sum over ranks of 8 consecutive elements starting at flat element index `elem` (a multiple of

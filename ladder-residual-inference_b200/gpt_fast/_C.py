@@ -64,6 +64,8 @@ _SIGNATURES = {
     "lri_comm_push": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "lri_add_rmsnorm_gather": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p,
                                        c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "lri_add_rmsnorm_allreduce": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p,
+                                          c_float, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "lri_lm_head_argmax_scratch_bytes": (c_size_t, []),
     "lri_lm_head_argmax": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p,
                                    c_size_t, c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_void_p]),

@@ -40,6 +40,9 @@ class NoComm:
     def can_split(self, count, rows=1, hidden=False):
         return False
 
+    def reduce_mode(self, count, rows=1, hidden=False):
+        return "kernel"
+
     def all_reduce_async(self, t, rows=None):
         return None
 
@@ -73,6 +76,9 @@ class TorchComm:
 
     def can_split(self, count, rows=1, hidden=False):
         return False
+
+    def reduce_mode(self, count, rows=1, hidden=False):
+        return "kernel"
 
     def __init__(self):
         self.world = dist.get_world_size()
@@ -187,9 +193,20 @@ class P2PComm:
         stand-alone kernel on the communication stream is already off the critical path and
         measured slightly faster (2 GPUs), so LRI_SPLIT_AR=auto keeps it; =1 forces the split
         path everywhere, =0 turns it off."""
-        if self.split_mode == "0" or (self.split_mode == "auto" and hidden):
+        if self.split_mode in ("0", "fused") or (self.split_mode == "auto" and hidden):
             return False
         return rows == 1 and count % 8 == 0 and count <= self._push_max
+
+    def reduce_mode(self, count, rows=1, hidden=False):
+        """How the partial of a row-parallel projection of `count` elements becomes a sum:
+        "kernel"  the all-reduce kernel (on the communication stream when the schedule hides it),
+        "split"   pushed from the projection's epilogue, reduced inside the consuming add + RMSNorm,
+        "fused"   pushed AND reduced inside the consuming add + RMSNorm (one launch, no stream hop;
+                  any number of rows while the message fits a push channel).
+        LRI_SPLIT_AR = auto | 0 | 1 | fused selects; every rank must use the same value."""
+        if self.split_mode == "fused":
+            return "fused" if (count % 8 == 0 and count <= self._push_max) else "kernel"
+        return "split" if self.can_split(count, rows, hidden) else "kernel"
 
     def linear_push(self, x, w, out, rows, channel, addend=None):
         """out = x W^T (+ addend) with the result also pushed to the peers on `channel`."""
@@ -205,13 +222,15 @@ class P2PComm:
         self._C.check(self._C.lib.lri_comm_push(self.handle, channel, self._C.dtype_code(t.dtype), t.data_ptr(), count,
                                                 torch.cuda.current_stream().cuda_stream))
 
-    def add_rmsnorm_gather(self, residual, ch1, add1, ch2, add2, weight, eps, residual_out, normed_out, rows, scale=1.0):
-        """lri_add_rmsnorm with addends summed over the ranks' pushed messages (channel > 0)."""
+    def add_rmsnorm_gather(self, residual, ch1, add1, ch2, add2, weight, eps, residual_out, normed_out, rows, scale=1.0,
+                           self_push=False):
+        """lri_add_rmsnorm with addends summed over the ranks' messages on a channel (> 0): messages
+        pushed beforehand, or with self_push stored to the peers by the same kernel."""
         C = self._C
-        C.check(C.lib.lri_add_rmsnorm_gather(self.handle, C.dtype_code(residual.dtype), residual.data_ptr(), ch1,
-                                             C.ptr(add1), ch2, C.ptr(add2), float(scale), C.ptr(weight), float(eps),
-                                             C.ptr(residual_out), C.ptr(normed_out), rows, residual.shape[-1],
-                                             self.timeout_ms, torch.cuda.current_stream().cuda_stream))
+        fn = C.lib.lri_add_rmsnorm_allreduce if self_push else C.lib.lri_add_rmsnorm_gather
+        C.check(fn(self.handle, C.dtype_code(residual.dtype), residual.data_ptr(), ch1, C.ptr(add1), ch2, C.ptr(add2),
+                   float(scale), C.ptr(weight), float(eps), C.ptr(residual_out), C.ptr(normed_out), rows,
+                   residual.shape[-1], self.timeout_ms, torch.cuda.current_stream().cuda_stream))
 
     def status(self):
         """Raises if a bounded peer wait gave up since the last check.  Waits for the compute stream

@@ -43,6 +43,7 @@ class Engine:
         self.ops = ops
         self.comm = comm if comm is not None else make_comm()
         self.ready = False
+        self._norm_pushes = False  # set per step by _reduce_plan
 
     # ------------------------------------------------------------------------------------------
     def setup(self, max_batch, max_seq, device, dtype):
@@ -129,9 +130,22 @@ class Engine:
         if (ch1 and add1 is not None) or (ch2 and add2 is not None):
             self.comm.add_rmsnorm_gather(self.resid, ch1 if add1 is not None else 0, add1,
                                          ch2 if add2 is not None else 0, add2, weight, self.cfg.norm_eps, res_out, out,
-                                         rows, scale)
+                                         rows, scale, self_push=self._norm_pushes)
         else:
             self.ops.add_rmsnorm(self.resid, add1, add2, weight, self.cfg.norm_eps, res_out, out, rows, scale)
+
+    def _reduce_plan(self, rows, hidden=False):
+        """(ca, cm, pa, pm, in_norm): the channels on which the norms gather the attention / MLP partial
+        (0: they read an all-reduced buffer), the channels on which the projections push from their
+        epilogue (0: they do not; with the fused form the norm pushes itself), and whether the
+        reduction happens inside the norm at all."""
+        mode = self.comm.reduce_mode(rows * self.d, rows, hidden=hidden)
+        self._norm_pushes = mode == "fused"
+        if mode == "kernel":
+            return 0, 0, 0, 0, False
+        if mode == "split":
+            return 1, 2, 1, 2, True
+        return 1, 2, 0, 0, True
 
     def _issue(self, buf, rows, channel, split):
         """Start the all-reduce of a partial.  Split form: the projection has pushed it already and the
@@ -283,18 +297,17 @@ class Engine:
         if S == 1 and self.overlap_sublayers:
             return self._run_ladder_two_streams(rows, B, S, pos)
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d, rows, hidden=True)
-        ca, cm = (1, 2) if split else (0, 0)
+        ca, cm, pa, pm, split = self._reduce_plan(rows, hidden=True)
         h_a = h_m = None
         first = True
         for layer in m.layers:
             comm.wait(h_a)
             self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=pa)
             h_a = self._issue(self.part_a, rows, 1, split)
             comm.wait(h_m)
             self._norm(layer.ffn_norm.weight, rows, add1=None if first else self.part_m, ch1=cm)
-            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=cm)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=pm)
             h_m = self._issue(self.part_m, rows, 2, split)
             first = False
         comm.wait(h_a)
@@ -312,8 +325,7 @@ class Engine:
         with the side add of layer i ordered after the main add of layer i and before the main add
         of layer i+1 by events."""
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d, rows, hidden=True)
-        ca, cm = (1, 2) if split else (0, 0)
+        ca, cm, pa, pm, split = self._reduce_plan(rows, hidden=True)
         main = torch.cuda.current_stream()
         side = self.side_stream
         ev = self._events
@@ -328,7 +340,7 @@ class Engine:
             comm.wait(h_a)
             self._norm(layer.attention_norm.weight, rows, add1=None if first else self.part_a, ch1=ca)
             e_attn_add.record(main)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=pa)
             h_a = self._issue(self.part_a, rows, 1, split)
             with torch.cuda.stream(side):
                 side.wait_event(e_attn_add)
@@ -337,7 +349,7 @@ class Engine:
                            ch1=cm)
                 e_mlp_add.record(side)
                 self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m,
-                          normed=self.normed_m, push=cm)
+                          normed=self.normed_m, push=pm)
                 h_m = self._issue(self.part_m, rows, 2, split)
             main.wait_event(e_mlp_add)  # the next attention add reads the residual the MLP add wrote
             first = False
@@ -391,23 +403,21 @@ class Engine:
 
     def _run_dense(self, rows, B, S, pos):
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d, rows)
-        ca, cm = (1, 2) if split else (0, 0)
+        ca, cm, pa, pm, split = self._reduce_plan(rows)
         pending = None
         for layer in m.layers:
             self._norm(layer.attention_norm.weight, rows, add1=pending, ch1=cm)
-            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=ca)
+            self._attention(layer.attention, layer.attention.wqkv.weight, rows, B, S, pos, self.part_a, push=pa)
             self._reduce_now(self.part_a, rows, 1, split)
             self._norm(layer.ffn_norm.weight, rows, add1=self.part_a, ch1=ca)
-            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=cm)
+            self._mlp(layer.feed_forward.w1.weight, layer.feed_forward.w2.weight, rows, self.part_m, push=pm)
             self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)
 
     def _run_parallel(self, rows, B, S, pos):
         comm, m = self.comm, self.model
-        split = comm.can_split(rows * self.d, rows)
-        cm = 2 if split else 0
+        _, cm, _, pm, split = self._reduce_plan(rows)
         pending = None
         for layer in m.layers:
             att = layer.attention
@@ -415,7 +425,7 @@ class Engine:
             w = att.wqkv1.weight
             nqkv = att.qkv_rows
             self._attention(att, w[:nqkv], rows, B, S, pos, self.part_a)
-            self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a, push=cm)
+            self._mlp(w[nqkv:], att.w2.weight, rows, self.part_m, addend=self.part_a, push=pm)
             self._reduce_now(self.part_m, rows, 2, split)
             pending = self.part_m
         self._norm(m.norm.weight, rows, add1=pending, write_residual=False, ch1=cm)

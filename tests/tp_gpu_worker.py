@@ -236,44 +236,47 @@ def check_models(comm_name, split=True):
 
 
 def check_split_single_row():
-    """Single-sequence decode takes the split all-reduce (pushed from the projection's epilogue,
-    reduced inside the next add + RMSNorm).  It must reproduce the stand-alone all-reduce kernel
-    bit for bit (both sum in rank order in fp32 and round once) and match the bf16 oracle."""
-    cfgs = {}
+    """Decode steps with the all-reduce folded into its neighbours: the split form (pushed from the
+    projection's epilogue, reduced inside the next add + RMSNorm; one sequence) and the fused form
+    (pushed and reduced inside the add + RMSNorm; one or two sequences).  Each must reproduce the
+    stand-alone all-reduce kernel bit for bit (all sum in rank order in fp32 and round once) and
+    match the bf16 oracle."""
     for family in ("ladder", "dense", "parallel"):
         cfg = gu.tiny_config(family)
         full = lo.make_full_weights(cfg, gu.SEED, **gu.INITS["loud"])
         g = torch.Generator().manual_seed(7)
-        prompt = torch.randint(0, cfg.vocab_size, (1, gu.PROMPT), generator=g)
-        outs = {}
-        for split in (True, False):
-            os.environ["LRI_COMM"] = "p2p"
-            os.environ["LRI_SPLIT_AR"] = "1" if split else "0"
-            comm_mod.reset_comm()
-            model = build(family, cfg, full, torch.bfloat16, "tiny-golden")
-            steps = []
-            with torch.no_grad():
-                logits = model(prompt.to(dev), torch.arange(gu.PROMPT, device=dev))
-                steps.append(logits[:, -1].float().cpu())
-                tok = logits[:, -1].argmax(-1, keepdim=True).to(torch.int32)
-                for n in range(3):
-                    pos = torch.tensor([gu.PROMPT + n], dtype=torch.int32, device=dev)
-                    logits = model(tok, pos)
+        for B in (1, 2):
+            prompt = torch.randint(0, cfg.vocab_size, (B, gu.PROMPT), generator=g)
+            outs = {}
+            for mode in ("0", "1", "fused"):
+                os.environ["LRI_COMM"] = "p2p"
+                os.environ["LRI_SPLIT_AR"] = mode
+                comm_mod.reset_comm()
+                model = build(family, cfg, full, torch.bfloat16, "tiny-golden")
+                steps = []
+                with torch.no_grad():
+                    logits = model(prompt.to(dev), torch.arange(gu.PROMPT, device=dev))
                     steps.append(logits[:, -1].float().cpu())
                     tok = logits[:, -1].argmax(-1, keepdim=True).to(torch.int32)
-            model._engine.comm.status()
-            outs[split] = torch.stack(steps)
-        assert torch.equal(outs[True], outs[False]), f"{family}: split and stand-alone all-reduce differ"
-        oracle = lo.OracleModel(family, cfg, full, world, torch.bfloat16, 1, gu.PROMPT + gu.NEW)
-        ref = [oracle.forward(prompt, torch.arange(gu.PROMPT))[:, -1].float()]
-        tok = outs[True][0].argmax(-1, keepdim=True)
-        for n in range(3):
-            ref.append(oracle.forward(tok, torch.tensor([gu.PROMPT + n]))[:, -1].float())
-            tok = outs[True][n + 1].argmax(-1, keepdim=True)
-        err = gu.rel_err(outs[True], torch.stack(ref))
-        assert err < 2e-2, f"{family} single-row decode vs oracle: {err:.3e}"
+                    for n in range(3):
+                        pos = torch.tensor([gu.PROMPT + n], dtype=torch.int32, device=dev)
+                        logits = model(tok, pos)
+                        steps.append(logits[:, -1].float().cpu())
+                        tok = logits[:, -1].argmax(-1, keepdim=True).to(torch.int32)
+                model._engine.comm.status()
+                outs[mode] = torch.stack(steps)
+            assert torch.equal(outs["1"], outs["0"]), f"{family} B={B}: split and stand-alone all-reduce differ"
+            assert torch.equal(outs["fused"], outs["0"]), f"{family} B={B}: fused and stand-alone all-reduce differ"
+            oracle = lo.OracleModel(family, cfg, full, world, torch.bfloat16, B, gu.PROMPT + gu.NEW)
+            ref = [oracle.forward(prompt, torch.arange(gu.PROMPT))[:, -1].float()]
+            tok = outs["0"][0].argmax(-1, keepdim=True)
+            for n in range(3):
+                ref.append(oracle.forward(tok, torch.tensor([gu.PROMPT + n]))[:, -1].float())
+                tok = outs["0"][n + 1].argmax(-1, keepdim=True)
+            err = gu.rel_err(outs["0"], torch.stack(ref))
+            assert err < 2e-2, f"{family} B={B} decode vs oracle: {err:.3e}"
     os.environ["LRI_SPLIT_AR"] = "1"
-    log("split all-reduce (single-row decode) ok")
+    log("split and fused all-reduce (decode) ok")
 
 
 def check_graph_with_comm():
