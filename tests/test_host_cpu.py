@@ -226,6 +226,33 @@ def test_message_size_threshold_and_elided_comm():
     e = ElidedComm(8, 3, like=Like)
     assert (e.world, e.rank, e.handle, e.timeout_ms) == (8, 3, Like.handle, 123)
     assert e.all_reduce_async(None) is None and e.wait(None) is None and not e.can_split(8, 1)
+    assert e.reduce_mode(4096, 1, hidden=True) == "kernel"
+
+
+def test_reduce_mode_selection():
+    """How a row-parallel partial becomes a sum, by LRI_SPLIT_AR value, message size and schedule: the stand-alone
+    all-reduce kernel, the split form (single-row decode only) or the one-kernel form (any rows while the message
+    fits a push channel)."""
+    from gpt_fast.comm import P2PComm
+
+    class Stub:
+        _push_max = 64 * 1024
+        can_split = P2PComm.can_split
+        reduce_mode = P2PComm.reduce_mode
+
+        def __init__(self, mode):
+            self.split_mode = mode
+
+    auto, off, on, fused = Stub("auto"), Stub("0"), Stub("1"), Stub("fused")
+    assert auto.reduce_mode(4096, 1, hidden=True) == "kernel"      # ladder: hidden behind the other sublayer
+    assert auto.reduce_mode(4096, 1, hidden=False) == "split"      # dense / parallel single-row decode
+    assert auto.reduce_mode(16 * 4096, 16, hidden=False) == "kernel"
+    assert off.reduce_mode(4096, 1) == "kernel"
+    assert on.reduce_mode(4096, 1, hidden=True) == "split" and on.reduce_mode(2 * 4096, 2, hidden=True) == "kernel"
+    assert fused.reduce_mode(4096, 1, hidden=True) == "fused" and fused.reduce_mode(16 * 4096, 16) == "fused"
+    assert fused.reduce_mode(16384 * 4096, 16384) == "kernel"      # a prompt pass does not fit a push channel
+    assert fused.reduce_mode(4100, 1) == "kernel"                  # not a multiple of 8 elements
+    assert not fused.can_split(4096, 1)
 
 
 def test_model_args_from_hf_config(tmp_path):
