@@ -72,6 +72,26 @@ __global__ void __launch_bounds__(kClThreads) attn_decode_cluster_kernel(const C
   float* g_m = g_o + kClMaxSplits * GT * HD;  // [16][GT]
   float* g_l = g_m + kClMaxSplits * GT;       // [16][GT]
 
+  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
+  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
+  {
+    // While the preceding kernel (the QKV projection) still runs: ask the L2 for this CTA's share of the
+    // cache, so that the loads below cost an L2 round trip instead of a DRAM one.  All rows but the newest
+    // were written by earlier steps.  The position read here may still be the previous step's; it only
+    // steers a hint (clamped to the cache), and the L2 is shared, so it does not matter which CTA asks.
+    int64_t hint = (p.pos_is_i64 ? *reinterpret_cast<const volatile int64_t*>(p.input_pos)
+                                 : static_cast<int64_t>(*reinterpret_cast<const volatile int32_t*>(p.input_pos))) + 2;
+    hint = hint < 0 ? 0 : (hint > p.smax ? p.smax : hint);
+    const int64_t hchunk = (hint + ns - 1) / ns;
+    const int64_t h0 = split * hchunk;
+    const int64_t h1 = (h0 + hchunk < hint) ? h0 + hchunk : hint;
+    if ((sl & 7) == 0) {  // one request per 128-byte line
+      for (int64_t j = h0 + rg; j < h1; j += NRG) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(kbase + j * HD));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vbase + j * HD));
+      }
+    }
+  }
   pdl_launch_dependents();
   pdl_wait();  // q and the newest cache row come from the preceding kernel
   int64_t ctx = load_pos(p.input_pos, p.pos_is_i64, 0) + 1;
@@ -87,8 +107,6 @@ __global__ void __launch_bounds__(kClThreads) attn_decode_cluster_kernel(const C
   const int64_t chunk = (ctx + ns - 1) / ns;
   const int64_t p0 = split * chunk;
   const int64_t p1 = (p0 + chunk < ctx) ? p0 + chunk : ctx;
-  const T* kbase = static_cast<const T*>(p.k_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
-  const T* vbase = static_cast<const T*>(p.v_cache) + (static_cast<int64_t>(b) * p.n_kv + kvh) * p.smax * HD + sl * 8;
 
   float m[GT], l[GT], acc[GT][8];
 #pragma unroll

@@ -199,7 +199,7 @@ def test_qkv_rope_kvcache(dtype, B, S, nh, nkv, hd, gathered):
 @pytest.mark.parametrize("B", [1, 3])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 64), (8, 1, 128), (4, 4, 128), (6, 2, 64), (32, 8, 128)])
 @pytest.mark.parametrize("pos,splits", [(0, 1), (5, 4), (63, 3), (200, 7), (255, 64), (130, 1), (100, 8), (17, 2),
-                                        (3, 8)])
+                                        (3, 8), (250, 16), (40, 16), (7, 16)])
 def test_attn_decode(dtype, B, nh, nkv, hd, pos, splits):
     smax, bmax = 256, 3
     g = torch.Generator().manual_seed(nh * 10 + pos)
