@@ -62,7 +62,8 @@ int lri_set_gemm_backend(int backend);
  * (LRI_ATTN_CLUSTER: 0, 1), attn_mma (LRI_ATTN_MMA: -1 choose, 0, 1), decode_splits
  * (LRI_DECODE_SPLITS: 0 choose, 1..64), attn_prefill_tc (LRI_ATTN_PREFILL_TC: 0 mma.sync kernel, 1 tcgen05
  * kernel), gemm_reserve_sms (LRI_GEMM_RESERVE_SMS: SMs
- * the persistent prefill GEMM leaves free for a collective running beside it, 0..64).  Unknown
+ * the persistent prefill GEMM leaves free for a collective running beside it, 0..64), attn_head_tile
+ * (LRI_ATTN_HEAD_TILE: query heads of a KV group per CTA of the cluster decode attention, 0 choose, 1, 2, 4).  Unknown
  * names and values an option does not take return LRI_ERR_ARG.  No counterpart in the reference
  * (its only switches are benchmark.py's command-line flags). */
 int lri_set_option(const char* name, int value);

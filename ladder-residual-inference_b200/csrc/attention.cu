@@ -10,6 +10,7 @@
 namespace lri {
 // cluster form of the decode kernel (attention_cluster.cu)
 bool attn_decode_cluster_supports(int num_splits);
+int attn_decode_cluster_head_tile(int B, int n_kv, int g);
 int attn_decode_cluster_launch(int dtype, const void* q, const void* k_cache, const void* v_cache,
                                const void* input_pos, int pos_is_i64, void* out, int B, int n_head, int n_kv,
                                int head_dim, int64_t smax, int num_splits, float scale_log2, cudaStream_t st);
@@ -882,15 +883,16 @@ extern "C" int lri_attn_decode_plan(int B, int n_head, int n_kv, int head_dim, i
     *num_splits = (static_cast<int64_t>(B) * n_kv < 2 * sms && smax >= 256) ? 2 : 1;
     return LRI_OK;
   }
-  const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
+  const int gt = attn_decode_cluster_head_tile(B, n_kv, g);
   const int64_t base = static_cast<int64_t>(B) * n_kv * (g / gt);
   const int64_t want = (2 * sms + base - 1) / base;
   const int64_t bytes_per_cta_at_8 = smax * head_dim * 2 * 2 / 8;
   if (want <= 8 || bytes_per_cta_at_8 <= (1 << 20)) {
-    // clusters of 16 (the opt-in maximum) only for one or two clusters, i.e. a one-KV-head shard of a single
-    // sequence (measured on B200, context 1152: 5.4 vs 6.7 us); with 8 clusters they are slower than 8 both
-    // alone (10.0 vs 8.3 us) and next to the MLP chain they share the SMs with
-    const int64_t cap = (base <= 2 && attn_decode_cluster_supports(16)) ? 16 : 8;
+    // clusters of 16 (the opt-in maximum) only for up to four clusters, i.e. a shard of one or two KV heads of
+    // a single sequence with its query heads spread over the clusters (measured on B200, context 1152, one
+    // cluster: 5.4 vs 6.7 us); with 8 clusters they are slower than 8 both alone (10.0 vs 8.3 us) and next to
+    // the MLP chain they share the SMs with
+    const int64_t cap = (base <= 4 && attn_decode_cluster_supports(16)) ? 16 : 8;
     int n = 1;
     const int64_t lim = want < cap ? want : cap;
     while (n * 2 <= lim && smax / (n * 2) >= 32) n *= 2;

@@ -21,6 +21,8 @@
 namespace cg = cooperative_groups;
 
 namespace lri {
+int attn_decode_cluster_head_tile(int B, int n_kv, int g);
+
 namespace {
 
 constexpr int kClWarps = 8;
@@ -274,7 +276,7 @@ int launch_u(const ClusterDecodeParams& p, int B, int ns, int tiles, cudaStream_
 template <typename T, int HD>
 int launch_hd(const ClusterDecodeParams& p, int B, int ns, cudaStream_t st) {
   const int g = p.n_head / p.n_kv;
-  const int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
+  const int gt = attn_decode_cluster_head_tile(B, p.n_kv, g);
   const int tiles = p.n_kv * (g / gt);
   if (gt == 4) return launch_u<T, HD, 4>(p, B, ns, tiles, st);
   if (gt == 2) return launch_u<T, HD, 2>(p, B, ns, tiles, st);
@@ -282,6 +284,20 @@ int launch_hd(const ClusterDecodeParams& p, int B, int ns, cudaStream_t st) {
 }
 
 }  // namespace
+
+// Query heads of a KV group that one CTA serves (the CTAs of a group's tiles read the same cache rows).
+// A thread's time goes into its dot products and their shuffles, GT of each per cache row, so with few
+// clusters in the grid (a small shard of one or two sequences) the heads are spread over more clusters
+// while at most 4 result: on the 8B shard of 1/8 (one KV head, 4 query heads, context 1152) 16-CTA
+// clusters take 5.40 us with 4 heads per CTA, 4.00 us with 2, 3.35 us with 1; on the 1/4 shard 5.41,
+// 4.13 and 4.19 us.  LRI_ATTN_HEAD_TILE=1|2|4 overrides.
+int attn_decode_cluster_head_tile(int B, int n_kv, int g) {
+  const int forced = option(OPT_ATTN_HEAD_TILE);
+  if (forced > 0 && g % forced == 0) return forced;
+  int gt = (g % 4 == 0) ? 4 : ((g % 2 == 0) ? 2 : 1);
+  while (gt > 1 && static_cast<int64_t>(B) * n_kv * (g / (gt / 2)) <= 4) gt /= 2;
+  return gt;
+}
 
 bool attn_decode_cluster_supports(int num_splits) {
   return option(OPT_ATTN_CLUSTER) != 0 &&

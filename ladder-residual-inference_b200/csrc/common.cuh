@@ -62,6 +62,7 @@ enum Option {
   OPT_DECODE_SPLITS,    // LRI_DECODE_SPLITS  fixed number of sequence ranges for decode attention (0 = choose)
   OPT_ATTN_PREFILL_TC,  // LRI_ATTN_PREFILL_TC  0: prefill attention on the mma.sync kernel; 1: tcgen05 / TMEM kernel (default)
   OPT_GEMM_RESERVE_SMS, // LRI_GEMM_RESERVE_SMS  SMs the persistent prefill GEMM leaves free (for a collective running beside it)
+  OPT_ATTN_HEAD_TILE,   // LRI_ATTN_HEAD_TILE  query heads per CTA of the cluster decode-attention kernel: 1, 2, 4 (0 = choose)
   OPT_COUNT
 };
 int option(int which);

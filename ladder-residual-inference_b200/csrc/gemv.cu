@@ -195,11 +195,13 @@ int launch_gemv(const LinearParams& p, cudaStream_t st) {
 
 // Rows per CTA.  A CTA keeps R * U = 16 / M-dependent 16-byte weight loads in flight per thread
 // whatever R is; fewer rows per CTA mean more, shorter CTAs (less wave quantisation on small
-// projections), more rows mean fewer reductions.  LRI_GEMV_R=2|4|8 overrides the choice.
+// projections), more rows mean fewer reductions.  Measured on the 8B shard shapes of 1, 2, 4 and 8
+// ranks, 4 rows win everywhere except for a very short K (the output projection of a 1/8 shard,
+// K = 512: one warp per CTA, 1.89 us with 8 rows against 2.21 us).  LRI_GEMV_R=2|4|8 overrides the choice.
 int rows_per_cta(const LinearParams& p) {
   const int forced = option(OPT_GEMV_R);
-  (void)p;
-  return forced ? forced : 4;
+  if (forced) return forced;
+  return p.k <= 512 ? 8 : 4;
 }
 
 template <typename T, int EPI>

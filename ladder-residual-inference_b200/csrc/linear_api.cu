@@ -44,6 +44,7 @@ const OptionSpec kOptionSpecs[OPT_COUNT] = {
     {"decode_splits", "LRI_DECODE_SPLITS", 0, 0, 64},
     {"attn_prefill_tc", "LRI_ATTN_PREFILL_TC", 1, 0, 1},
     {"gemm_reserve_sms", "LRI_GEMM_RESERVE_SMS", 0, 0, 64},
+    {"attn_head_tile", "LRI_ATTN_HEAD_TILE", 0, 0, 4},
 };
 
 bool option_value_ok(int which, int v) {
@@ -52,6 +53,7 @@ bool option_value_ok(int which, int v) {
   if (which == OPT_GEMV_R) return v == 0 || v == 2 || v == 4 || v == 8;
   if (which == OPT_GEMV_U) return v == 0 || v == 2;
   if (which == OPT_GEMV_MT) return v == 0 || v == 1 || v == 2 || v == 4;
+  if (which == OPT_ATTN_HEAD_TILE) return v == 0 || v == 1 || v == 2 || v == 4;
   return true;
 }
 

@@ -104,6 +104,34 @@ def test_linear_gemv(dtype, m, n, k):
     _ulp_close(y, lo.linear(x, w) + add, dtype, ulps=6)
 
 
+@pytest.mark.parametrize("rows_per_cta,depth", [(2, 0), (8, 0), (4, 2), (0, 0)])
+@pytest.mark.parametrize("m", [1, 4, 8])
+def test_linear_gemv_tuning_options(rows_per_cta, depth, m):
+    """The streaming kernel's tuning options (weight rows per CTA, loads in flight per thread) change the launch
+    shape, not the result: every setting against the oracle, including the short-K shapes for which the library
+    itself picks 8 rows per CTA."""
+    C = _C()
+    try:
+        assert C.lib.lri_set_option(b"gemv_rows_per_cta", rows_per_cta) == 0
+        assert C.lib.lri_set_option(b"gemv_depth", depth) == 0
+        for n, k in [(4096, 512), (1000, 256), (520, 4096), (4096, 1792)]:
+            g = torch.Generator().manual_seed(m + n + k)
+            x = _randn(g, m, k)
+            w = _randn(g, n, k, scale=1 / math.sqrt(k))
+            y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            _ops().linear(x.cuda(), w.cuda(), y, m)
+            _ulp_close(y, lo.linear(x, w), torch.bfloat16)
+            inter = n // 2 // 8 * 8
+            h = torch.empty(m, inter, dtype=torch.bfloat16, device="cuda")
+            ws = torch.empty(max(_ops().gateup_workspace_bytes(m, inter), 16), dtype=torch.uint8, device="cuda")
+            w1 = (w[: 2 * inter] * 2).contiguous()
+            _ops().gateup_swiglu(x.cuda(), w1.cuda(), h, m, ws)
+            _ulp_close(h, lo.swiglu(lo.linear(x, w1)), torch.bfloat16, ulps=8)
+    finally:
+        C.lib.lri_set_option(b"gemv_rows_per_cta", 0)
+        C.lib.lri_set_option(b"gemv_depth", 0)
+
+
 GEMM_M = [9, 16, 24, 33, 64, 65, 128, 200, 300]
 GEMM_NK = [(64, 64), (136, 72), (512, 256), (1000, 4096), (384, 1024)]
 
