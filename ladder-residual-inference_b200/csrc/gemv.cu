@@ -208,11 +208,11 @@ template <typename T, int EPI>
 int dispatch_m(const LinearParams& p, cudaStream_t st) {
   const int r = rows_per_cta(p);
   // Half the loads in flight per thread: fewer registers, more resident CTAs.  For one token row it wins where a
-  // long K meets few CTAs (up to 6144 weight rows): 8B w2 21.95 -> 20.32 us (K = 14336), its half shard 11.94 ->
-  // 10.94 us (K = 7168), QKV and wo at K = 4096 by 0.15-0.2 us, and the whole one-GPU decode step by 1.9 %;
-  // shorter K (the 1/4 and 1/8 shards) and wider projections are unchanged or slightly slower with it.
-  // LRI_GEMV_U=2 forces it for every one-row projection.
-  const bool half_depth = option(OPT_GEMV_U) == 2 || (p.k >= 4096 && p.n <= 6144);
+  // long K meets 3072..6144 weight rows: 8B w2 21.95 -> 20.32 us (K = 14336), its half shard 11.94 -> 10.94 us
+  // (K = 7168), QKV and wo at K = 4096 by 0.15-0.2 us, and the whole one-GPU decode step by 1.9 %; shorter K (the
+  // 1/4 and 1/8 shards) and wider projections are unchanged or slightly slower with it, and the 2048-row w2 of
+  // the 1B shape loses about 1 us.  LRI_GEMV_U=2 forces it for every one-row projection.
+  const bool half_depth = option(OPT_GEMV_U) == 2 || (p.k >= 4096 && p.n >= 3072 && p.n <= 6144);
   if (half_depth && p.m <= 1 && r == 4) return launch_gemv<T, 1, 4, 2, EPI>(p, st);
 #define LRI_GEMV_CASE(M_, U2, U4, U8)                                   \
   if (p.m <= M_) {                                                      \
