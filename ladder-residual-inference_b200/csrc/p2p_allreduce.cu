@@ -85,27 +85,36 @@ __global__ void __launch_bounds__(kArThreads) allreduce_ll_kernel(const ArParams
       if (r != p.rank) st_volatile16(p.inbox[r] + my_slot + u * 16, line);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const uint8_t* lines = mine + region + static_cast<size_t>(buf) * p.world * kLlSlotBytes + u * 16;
-    // first look at all peers' lines at once (independent loads), then re-poll only the late ones
+    // Look at all peers' lines at once (independent loads), then keep re-reading ALL lines that are still
+    // late in one round of independent loads per iteration.  Re-polling peer after peer costs one L2 round
+    // trip per late peer in sequence (measured: 4.4 us at 2 ranks, 7.7 us at 8, about 0.55 us per extra
+    // peer); polled together the wait is the latest arrival plus one round trip.
     uint4 got[kMaxWorld];
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
       if (r < p.world && r != p.rank) got[r] = ld_volatile16(lines + static_cast<size_t>(r) * kLlSlotBytes);
+    unsigned int spins = 0;
+    while (!gave_up) {
+      bool late = false;
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r)
+        if (r < p.world && r != p.rank && (got[r].y != epoch || got[r].w != epoch)) late = true;
+      if (!late) break;
+      if ((++spins & 63u) == 0u && global_ns() - t0 > p.timeout_ns) {
+        gave_up = true;
+        atomicExch(&ctl->status, LRI_ERR_TIMEOUT);
+        break;
+      }
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r)
+        if (r < p.world && r != p.rank && (got[r].y != epoch || got[r].w != epoch))
+          got[r] = ld_volatile16(lines + static_cast<size_t>(r) * kLlSlotBytes);
+    }
+    // sum in rank order (this rank's own contribution comes from registers)
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r) {
       if (r >= p.world) continue;
-      uint2 payload = own;
-      if (r != p.rank) {
-        unsigned int spins = 0;
-        while (!gave_up && (got[r].y != epoch || got[r].w != epoch)) {
-          if ((++spins & 63u) == 0u && global_ns() - t0 > p.timeout_ns) {
-            gave_up = true;
-            atomicExch(&ctl->status, LRI_ERR_TIMEOUT);
-            break;
-          }
-          got[r] = ld_volatile16(lines + static_cast<size_t>(r) * kLlSlotBytes);
-        }
-        payload = make_uint2(got[r].x, got[r].z);
-      }
+      const uint2 payload = (r == p.rank) ? own : make_uint2(got[r].x, got[r].z);
       float lo0, hi0, lo1, hi1;
       Num<T>::unpack2(payload.x, lo0, hi0);
       Num<T>::unpack2(payload.y, lo1, hi1);
