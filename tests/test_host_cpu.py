@@ -110,6 +110,8 @@ def test_decode_splits_choice():
     assert decode_splits(16, 32, 8, 1288) == 2          # 128 (sequence, KV head) pairs: tensor-core kernel, two ranges
     assert decode_splits(64, 32, 8, 1288) == 1          # 512 pairs: one range each
     assert decode_splits(64, 4, 1, 1288) == 4           # TP=8 shard: below 128 pairs, the cluster kernel
+    # single sequence: up to four clusters (query heads spread over them) take the 16-CTA cluster, eight do not
+    assert [decode_splits(1, 32 // t, 8 // t, 1288) for t in (1, 2, 4, 8)] == [8, 16, 16, 16]
     try:
         _C.check(_C.lib.lri_set_option(b"attn_mma", 0))
         assert decode_splits(64, 32, 8, 1288) == 1 and decode_splits(16, 32, 8, 1288) == 2   # the cluster kernel's own choice
@@ -129,6 +131,8 @@ def test_options_table():
     assert v.value == 8
     assert _C.lib.lri_set_option(b"stream_rows", 17) == -1 and _C.lib.lri_set_option(b"no_such_option", 1) == -1
     assert _C.lib.lri_set_option(b"gemv_rows_per_cta", 3) == -1
+    assert _C.lib.lri_set_option(b"attn_head_tile", 3) == -1 and _C.lib.lri_set_option(b"attn_head_tile", 2) == 0
+    _C.check(_C.lib.lri_set_option(b"attn_head_tile", 0))
     _C.check(_C.lib.lri_set_option(b"stream_rows", 4))
     _C.check(_C.lib.lri_get_option(b"stream_rows", ctypes.byref(v)))
     assert v.value == 4
