@@ -191,9 +191,12 @@ class P2PComm:
         decode steps, where the fused push exists; larger steps use the all-reduce kernel.
         `hidden` says that the schedule consumes the sum a sublayer later (ladder): there the
         stand-alone kernel on the communication stream is already off the critical path and
-        measured slightly faster (2 GPUs), so LRI_SPLIT_AR=auto keeps it; =1 forces the split
-        path everywhere, =0 turns it off."""
-        if self.split_mode in ("0", "fused") or (self.split_mode == "auto" and hidden):
+        measured faster (2 ranks: slightly; 8 ranks: 1262 against 900 tokens/s).  The gathering norm
+        polls its peers one after the other, so its cost grows with the number of ranks: with
+        LRI_SPLIT_AR=auto the split path is taken only by the schedules that consume the sum at once
+        and only at 2 ranks, where it was measured faster than kernel + norm; =1 forces it everywhere
+        it exists, =0 turns it off, =fused selects the one-kernel form (see reduce_mode)."""
+        if self.split_mode in ("0", "fused") or (self.split_mode == "auto" and (hidden or self.world > 2)):
             return False
         return rows == 1 and count % 8 == 0 and count <= self._push_max
 

@@ -244,13 +244,15 @@ def test_reduce_mode_selection():
         can_split = P2PComm.can_split
         reduce_mode = P2PComm.reduce_mode
 
-        def __init__(self, mode):
-            self.split_mode = mode
+        def __init__(self, mode, world=2):
+            self.split_mode, self.world = mode, world
 
     auto, off, on, fused = Stub("auto"), Stub("0"), Stub("1"), Stub("fused")
     assert auto.reduce_mode(4096, 1, hidden=True) == "kernel"      # ladder: hidden behind the other sublayer
     assert auto.reduce_mode(4096, 1, hidden=False) == "split"      # dense / parallel single-row decode
     assert auto.reduce_mode(16 * 4096, 16, hidden=False) == "kernel"
+    assert Stub("auto", world=8).reduce_mode(4096, 1, hidden=False) == "kernel"   # the gathering norm polls peer by peer
+    assert Stub("1", world=8).reduce_mode(4096, 1, hidden=False) == "split"
     assert off.reduce_mode(4096, 1) == "kernel"
     assert on.reduce_mode(4096, 1, hidden=True) == "split" and on.reduce_mode(2 * 4096, 2, hidden=True) == "kernel"
     assert fused.reduce_mode(4096, 1, hidden=True) == "fused" and fused.reduce_mode(16 * 4096, 16) == "fused"
